@@ -287,7 +287,9 @@ int gi_kv_store(void* qkv, int dtype, long ld, const void* first, const float* l
 // proj: the input projection's rows [tokens, 2 * inner + 2 * G * N + heads] = [z | x | B | C | dt], inner = heads * P.
 // conv: xbc_out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps - 1) + j, c]) over channels c of [x | B | C], inputs
 // before the step's first token from the state (zero for a fresh sequence); then the state takes the last taps - 1
-// inputs (gi_mamba2_conv_update, a launch of its own because it overwrites what the first reads).
+// inputs (gi_mamba2_conv_update, a launch of its own because it overwrites what the first reads).  Other mixers with a
+// short convolution use the two as they are: `inner` is the column of the rows where the `channels` convolved ones start
+// (0 and up), `s_floats` the floats of a state row before the convolution's inputs.
 int gi_mamba2_conv(void* xbc_out, const void* proj, int dtype, long ld_proj, const void* conv_w, const void* conv_b,
                    int w_dtype, const float* state, long state_ld, int state_rows, const int* cu_seqlens,
                    const int* seq_slots, int n_seqs, int max_q_len, int inner, int channels, int taps, int s_floats,
@@ -417,6 +419,42 @@ int gi_attn_combine(void* out, long ldo, int dtype, const float* part_o, const f
 
 int gi_sample(int* out_tokens, const float* logits, long ld, int n_rows, int vocab, float temperature, int top_k,
               float top_p, unsigned long long* rng_state, const int* state_index, void* stream);
+
+// ---- layers that read the stream itself and norm a sublayer's output (stream_parts.cu) ---------------------------------
+// out (activation type) = x (float32), n_values numbers.
+int gi_cast_rows(void* out, int out_dtype, const float* x, long n_values, void* stream);
+// x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w [* scale], float32 rows of d numbers; scale may be null.
+int gi_postnorm_add(float* x, const float* y, const void* w, const void* scale, int w_dtype, int n_rows, int d, float eps,
+                    void* stream);
+// out += alpha * a over n_values float32 numbers.
+int gi_axpy(float* out, const float* a, float alpha, long n_values, void* stream);
+// One token's float32 row [q: n_heads * hd | k: n_kv * hd | v: n_kv * hdv] (n_kv 0: queries only): biases (each may be
+// null), RMS norm over the whole of q and of k with weights wq / wk (null: no norm), rotation of the first 2 * half numbers
+// of every head by `table` [tokens][half] of (cos, sin) (adjacent: pairs (2i, 2i + 1); else (i, i + half)), q into q_out,
+// k and v into the token's place in the pages.
+int gi_qk_prepare(void* q_out, long ldq, int dtype, const float* in, long ld, const void* bq, const void* bk, const void* bv,
+                  const void* wq, const void* wk, int w_dtype, float eps, const float* table, int half, int adjacent,
+                  const int* positions, const int* slots, const int* block_table, int max_pages, void* kcache, void* vcache,
+                  int n_tokens, int n_heads, int n_kv, int hd, int hdv, int write_cache, void* stream);
+// out = a * sigmoid(g) (act 0) or a * silu(g) (act 1); a and out are contiguous [n_rows, f].
+int gi_gate_mul(void* out, const void* a, const void* g, long ldg, int dtype, int n_rows, int f, int act, void* stream);
+// out = y / sqrt(mean over each group of `group` values (y^2) + eps) * w * act(g); w has `group` values (w_per_row 0) or `inner`.
+int gi_norm_gate(void* out, int dtype, const float* y, const void* g, long ldg, const void* w, int w_dtype, int n_rows, int inner,
+                 int group, int w_per_row, int act, float eps, void* stream);
+// out[t, c] = gelu_tanh(gx[t, c]) * table[tokens[t], col0 + c], c < dim.
+int gi_side_gate(void* out, const void* gx, long ldg, int dtype, const void* table, long ld_table, int w_dtype, const int* tokens,
+                 int n_rows, int col0, int dim, void* stream);
+// out = gelu(in), the exact form, [n_rows, f].
+int gi_act_rows(void* out, const void* in, long ld_in, int dtype, int n_rows, int f, void* stream);
+
+// ---- linear attention with a matrix of state per head (linear_state.cu) -------------------------------------------------
+// o float32 [tokens, heads * V].  q, k: rows with qk_heads * K numbers at the pointer; v: heads * V.  a_in / b_in: rows with
+// one number per head (null: a constant decay decay_c[h] / no write strength).  With a_in, decay_c holds A_log.
+int gi_linear_state(float* o, const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const void* a_in,
+                    long lda, const void* b_in, long ldb, int dtype, const float* decay_c, const float* dt_bias, float* state,
+                    long state_ld, int state_rows, const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads,
+                    int qk_heads, int K, int V, int in_act, int unit_norm, float norm_eps, float q_scale, int delta,
+                    void* stream);
 
 #ifdef __cplusplus
 }

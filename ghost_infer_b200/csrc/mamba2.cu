@@ -263,7 +263,7 @@ extern "C" int gi_mamba2_conv(void* xbc_out, const void* proj, int dtype, long l
                               const int* cu_seqlens, const int* seq_slots, int n_seqs, int max_q_len, int inner,
                               int channels, int taps, int s_floats, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
-  if (taps < 1 || channels <= 0 || inner <= 0) return gi::fail(GI_ERR_ARG, "mamba2 conv: bad sizes");
+  if (taps < 1 || channels <= 0 || inner < 0) return gi::fail(GI_ERR_ARG, "mamba2 conv: bad sizes");
   if (n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: more than 65535 sequences in one launch");
   if ((channels + 255) / 256 > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: %d channels are more than one launch takes", channels);
   dim3 grid((max_q_len + 7) / 8, n_seqs, (channels + 255) / 256);

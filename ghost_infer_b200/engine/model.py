@@ -85,12 +85,16 @@ class Model:
             out.extend(layer.weights())
         out.extend(self.final_norm.weights())
         out.extend(self.head.weights())
-        seen = set()
+        seen: Dict[str, WeightSpec] = {}
+        kept = []
         for w in out:
-            if w.name in seen:
+            first = seen.get(w.name)
+            if first is None:
+                seen[w.name] = w
+                kept.append(w)
+            elif not (w.shared and first.shared and tuple(w.shape) == tuple(first.shape)):
                 raise ValueError(f"two parts claim the tensor \"{w.name}\"")
-            seen.add(w.name)
-        return out
+        return kept
 
     def ignorable_tensors(self) -> List[str]:
         out = list(self.head.ignorable()) if hasattr(self.head, "ignorable") else []

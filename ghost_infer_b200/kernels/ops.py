@@ -102,6 +102,15 @@ def _bind():
         "gi_attn_latent_tc": [P, L, P, P, P, L, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
         "gi_gemm_tc_bf16_bias": [P, I, P, P, P, I, I, I, L, L, L, I, P],
         "gi_moe_experts_tc_ungated": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
+        "gi_cast_rows": [P, I, P, L, P],
+        "gi_postnorm_add": [P, P, P, P, I, I, I, F, P],
+        "gi_axpy": [P, P, F, L, P],
+        "gi_qk_prepare": [P, L, I, P, L, P, P, P, P, P, I, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, I, P],
+        "gi_gate_mul": [P, P, P, L, I, I, I, I, P],
+        "gi_norm_gate": [P, I, P, P, L, P, I, I, I, I, I, I, F, P],
+        "gi_side_gate": [P, P, L, I, P, L, I, P, I, I, I, P],
+        "gi_act_rows": [P, P, L, I, I, I, P],
+        "gi_linear_state": [P, P, L, P, L, P, L, P, L, P, L, I, P, P, P, L, I, P, P, I, I, I, I, I, I, I, F, F, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -1859,3 +1868,177 @@ def attention_latent(qa: torch.Tensor, memory, step, n_heads: int, rank: int, ro
         _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), _i32(step.seq_pos0, "start positions"), step.n_seqs,
         step.max_q_len, n_heads, 1, hd, float(scale), 0, rank, 0.0, None, 0, hd, _stream()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Layers that read the stream itself and norm a sublayer's output; attention with normed, rotated queries and keys.
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream in the activation type; in the 32-bit path the stream itself."""
+    _cuda(x, "residual stream")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("the stream's rows must be contiguous float32")
+    if dtype == torch.float32:
+        return x.as_subclass(torch.Tensor) if type(x) is not torch.Tensor else x
+    lib = _bind()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(lib, lib.gi_cast_rows(out.data_ptr(), _dt(out, "rows"), x.data_ptr(), x.numel(), _stream()))
+    return out
+
+
+def postnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, scale: Optional[torch.Tensor] = None) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * weight [* scale] over float32 rows."""
+    lib = _bind()
+    _cuda(x, "residual stream")
+    _cuda(y, "sublayer output")
+    n, d = x.shape
+    if (x.dtype != torch.float32 or y.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous()
+            or tuple(y.shape) != (n, d)):
+        raise KernelError("the stream and the sublayer's output must be contiguous float32 rows of one shape")
+    for t, what in ((weight, "the norm's weight"), (scale, "the channel scale")):
+        if t is not None and (t.numel() != d or not t.is_contiguous() or t.dtype != weight.dtype):
+            raise KernelError(f"{what} must hold {d} values of the norm weight's type")
+    _check(lib, lib.gi_postnorm_add(x.data_ptr(), y.data_ptr(), weight.data_ptr(), scale.data_ptr() if scale is not None else None,
+                                    _dt(weight, "norm weight"), n, d, float(eps), _stream()))
+
+
+def axpy(out: torch.Tensor, a: torch.Tensor, alpha: float) -> None:
+    """out += alpha * a, float32."""
+    lib = _bind()
+    _cuda(out, "rows")
+    _cuda(a, "rows")
+    if out.dtype != torch.float32 or a.dtype != torch.float32 or out.shape != a.shape or not out.is_contiguous() or not a.is_contiguous():
+        raise KernelError("axpy takes two contiguous float32 tensors of one shape")
+    _check(lib, lib.gi_axpy(out.data_ptr(), a.data_ptr(), float(alpha), out.numel(), _stream()))
+
+
+def qk_prepare(rows: torch.Tensor, out_dtype: torch.dtype, biases, norm_weights, eps: float, table: Optional[torch.Tensor],
+               rot: int, adjacent: bool, step, memory, n_heads: int, n_kv: int, head_dim: int, v_dim: int) -> torch.Tensor:
+    """Float32 projection rows [q | k | v] (`n_kv` 0: queries only) to queries [tokens, heads * head_dim] of `out_dtype`,
+    with keys and values written to `memory`'s pages where the layer owns them.  `biases` (q, k, v) and `norm_weights`
+    (q, k) hold tensors or None."""
+    lib = _bind()
+    _cuda(rows, "projected rows")
+    n = rows.shape[0]
+    qd, kd, vw = n_heads * head_dim, n_kv * head_dim, n_kv * v_dim
+    if rows.dtype != torch.float32 or rows.shape[1] != qd + kd + vw:
+        raise KernelError(f"projected rows must be float32 and {qd + kd + vw} wide, got {rows.dtype} {tuple(rows.shape)}")
+    ld = _rows(rows, "projected rows")
+    write = bool(n_kv > 0 and memory.writes and memory.k is not None)
+    params = [t for t in tuple(biases) + tuple(norm_weights) if t is not None]
+    wdt = params[0].dtype if params else torch.float32
+    for t, size in zip(tuple(biases) + tuple(norm_weights), (qd, kd, vw, qd, kd)):
+        if t is not None and (t.dtype != wdt or t.numel() != size or not t.is_contiguous()):
+            raise KernelError("biases and norm weights must be contiguous, of one type and of their projection's width")
+    if write:
+        if memory.k.dtype != out_dtype or memory.v.dtype != out_dtype:
+            raise KernelError(f"the cache is {memory.k.dtype}, the step runs in {out_dtype}")
+        if (tuple(memory.k.shape[1:]) != (n_kv, 64, head_dim) or tuple(memory.v.shape[1:]) != (n_kv, 64, v_dim)
+                or not memory.k.is_contiguous() or not memory.v.is_contiguous()):
+            raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}] and [.., {v_dim}]")
+    half = rot // 2
+    if half and (table is None or table.dtype != torch.float32 or tuple(table.shape) != (n, half, 2) or not table.is_contiguous()):
+        raise KernelError(f"the table of angles must be contiguous float32 [{n}, {half}, 2]")
+    q = torch.empty((n, qd), dtype=out_dtype, device=rows.device)
+    bt = memory.block_table if memory is not None else None
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(lib, lib.gi_qk_prepare(
+        q.data_ptr(), qd, _dt(q, "queries"), rows.data_ptr(), ld, ptr(biases[0]), ptr(biases[1]), ptr(biases[2]),
+        ptr(norm_weights[0]), ptr(norm_weights[1]), _DT[wdt], float(eps), ptr(table) if half else None, half, int(bool(adjacent)),
+        _i32(step.positions, "positions"), _i32(step.token_slots, "slots"), _i32(bt, "block table") if write else None,
+        bt.shape[1] if (write and bt is not None) else 0, memory.k.data_ptr() if write else None,
+        memory.v.data_ptr() if write else None, n, n_heads, n_kv if write or n_kv == 0 else n_kv, head_dim, v_dim, int(write), _stream()))
+    return q
+
+
+def gate_mul(a: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch.Tensor:
+    """a * sigmoid(gate) or a * silu(gate); `gate` may be a view of wider rows."""
+    lib = _bind()
+    _cuda(a, "rows")
+    _cuda(gate, "gate rows")
+    if act not in ("sigmoid", "silu"):
+        raise KernelError(f"unknown gate \"{act}\" (sigmoid, silu)")
+    if a.dtype != gate.dtype or a.shape != gate.shape or not a.is_contiguous():
+        raise KernelError("gated rows must be contiguous and of the gate's type and shape")
+    out = torch.empty_like(a)
+    _check(lib, lib.gi_gate_mul(out.data_ptr(), a.data_ptr(), gate.data_ptr(), _rows(gate, "gate rows"), _dt(a, "rows"), a.shape[0],
+                                a.shape[1], 1 if act == "silu" else 0, _stream()))
+    return out
+
+
+def norm_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, group: int, eps: float, act: str,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """y / sqrt(mean over each group of `group` values (y^2) + eps) * weight * act(gate), the weight per value of a group
+    (`group` values) or of the row."""
+    lib = _bind()
+    _cuda(y, "recurrence output")
+    _cuda(gate, "gate rows")
+    n, inner = y.shape
+    if act not in ("sigmoid", "silu"):
+        raise KernelError(f"unknown gate \"{act}\" (sigmoid, silu)")
+    if y.dtype != torch.float32 or not y.is_contiguous() or gate.dtype != out_dtype or tuple(gate.shape) != (n, inner):
+        raise KernelError("the gated norm takes contiguous float32 rows and a gate of the output's type and the rows' shape")
+    if weight.numel() not in (group, inner) or not weight.is_contiguous():
+        raise KernelError(f"the norm's weight must hold {group} or {inner} values")
+    out = torch.empty((n, inner), dtype=out_dtype, device=y.device)
+    _check(lib, lib.gi_norm_gate(out.data_ptr(), _dt(out, "normed rows"), y.data_ptr(), gate.data_ptr(), _rows(gate, "gate rows"),
+                                 weight.data_ptr(), _dt(weight, "norm weight"), n, inner, int(group),
+                                 int(weight.numel() == inner and group != inner), 1 if act == "silu" else 0, float(eps), _stream()))
+    return out
+
+
+def side_gate(gx: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, col0: int, dim: int) -> torch.Tensor:
+    """gelu_tanh(gx) * table[tokens, col0 : col0 + dim], in gx's type."""
+    lib = _bind()
+    _cuda(gx, "gate rows")
+    _cuda(table, "side table")
+    n = gx.shape[0]
+    if gx.shape[1] != dim or table.dim() != 2 or col0 < 0 or col0 + dim > table.shape[1] or tokens.numel() != n:
+        raise KernelError("side gate: the gate rows, the table's slice and the tokens do not fit each other")
+    out = torch.empty((n, dim), dtype=gx.dtype, device=gx.device)
+    _check(lib, lib.gi_side_gate(out.data_ptr(), gx.data_ptr(), _rows(gx, "gate rows"), _dt(gx, "gate rows"), table.data_ptr(),
+                                 _rows(table, "side table"), _dt(table, "side table"), _i32(tokens, "tokens"), n, int(col0), int(dim),
+                                 _stream()))
+    return out
+
+
+def gelu_rows(rows: torch.Tensor) -> torch.Tensor:
+    """gelu in its exact (erf) form, in the rows' type."""
+    lib = _bind()
+    _cuda(rows, "rows")
+    out = torch.empty(rows.shape, dtype=rows.dtype, device=rows.device)
+    _check(lib, lib.gi_act_rows(out.data_ptr(), rows.data_ptr(), _rows(rows, "rows"), _dt(rows, "rows"), rows.shape[0], rows.shape[1],
+                                _stream()))
+    return out
+
+
+def linear_state(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, step, heads: int, qk_heads: int,
+                 key_dim: int, v_dim: int, decay: torch.Tensor, *, decay_in: Optional[torch.Tensor] = None,
+                 dt_bias: Optional[torch.Tensor] = None, beta_in: Optional[torch.Tensor] = None, in_act: bool = False,
+                 unit_norm: bool = False, norm_eps: float = 1e-6, q_scale: float = 1.0, delta: bool = False) -> torch.Tensor:
+    """The recurrence S <- g S; u = delta ? beta (v - S^T k) : v; S <- S + k u^T; o = S^T q over the step's tokens, from and
+    into `state` ([slots + 1, >= heads * key_dim * v_dim] float32).  q, k, v, decay_in, beta_in: views of rows in one type.
+    `decay` float32 [heads]: the decay itself, or A_log where `decay_in` (with `dt_bias`) gives the per-token part.
+    Returns float32 [tokens, heads * v_dim]."""
+    lib = _bind()
+    n = q.shape[0]
+    for t, what, width in ((q, "queries", qk_heads * key_dim), (k, "keys", qk_heads * key_dim), (v, "values", heads * v_dim),
+                           (decay_in, "decay rows", heads), (beta_in, "write strengths", heads)):
+        if t is None:
+            continue
+        _cuda(t, what)
+        if t.dtype != q.dtype or tuple(t.shape) != (n, width) or t.stride(1) != 1:
+            raise KernelError(f"{what} must be [{n}, {width}] rows of the queries' type, got {t.dtype} {tuple(t.shape)}")
+    if state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < heads * key_dim * v_dim:
+        raise KernelError("the recurrence needs its per-sequence state as a contiguous float32 matrix of at least heads x keys x values")
+    for t in (decay, dt_bias):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous() or not t.is_cuda):
+            raise KernelError(f"the recurrence's per-head constants must be {heads} float32 values on the device")
+    o = torch.empty((n, heads * v_dim), dtype=torch.float32, device=q.device)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    ldo = lambda t: t.stride(0) if t is not None else 0
+    _check(lib, lib.gi_linear_state(
+        o.data_ptr(), q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), ptr(decay_in), ldo(decay_in),
+        ptr(beta_in), ldo(beta_in), _dt(q, "queries"), decay.data_ptr(), ptr(dt_bias), state.data_ptr(), state.stride(0),
+        state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads, qk_heads, key_dim,
+        v_dim, int(in_act), int(unit_norm), float(norm_eps), float(q_scale), int(delta), _stream()))
+    return o

@@ -26,8 +26,8 @@ trash row, so indexing by the slot arrays needs no special case.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Any, List, Mapping, NamedTuple, Optional, Tuple
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, NamedTuple, Optional, Tuple
 
 import torch
 
@@ -38,6 +38,7 @@ class WeightSpec(NamedTuple):
     name: str                  # full tensor name in the weights file
     shape: Tuple[int, ...]
     init: str = "normal"       # how the random-weights mode fills it: "normal" or "ones"
+    shared: bool = False       # several parts may name this tensor (one table, read by every layer); it is loaded once
 
 
 @dataclass
@@ -46,6 +47,13 @@ class Runtime:
     cache: torch.bfloat16 (the serving path) or torch.float32 (everything in true 32-bit)."""
     device: torch.device
     dtype: torch.dtype
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)     # tensors several parts read: one device copy each
+
+    def place_shared(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        """A weight that several parts name: placed once, the same device tensor for all of them."""
+        if name not in self.shared:
+            self.shared[name] = self.place(t)
+        return self.shared[name]
 
     def place(self, t: torch.Tensor) -> torch.Tensor:
         """A weight on the device.  32-bit path: everything becomes float32.  bfloat16 path:

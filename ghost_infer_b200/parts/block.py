@@ -1,6 +1,8 @@
 """Arrangements of a layer's parts around the residual stream."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import Block
 from .registry import register
@@ -26,3 +28,27 @@ class PreNormResidual(Block):
         h = self.ffn_norm.forward(x)
         with ops.defer_into(x):
             self.ffn.forward(h, x, step)
+
+
+@register("block", "residual_postnorm")
+class ResidualPostNorm(Block):
+    """x += s1 * norm(mixer(x)); x += s2 * norm(ffn(x)): the sublayers read the stream itself (in the activation type)
+    and the norm sits on what they give back; s1 and s2 are learned per-channel scales (`extra["mixer_scale"]`,
+    `extra["ffn_scale"]`, each optional).  Then every `extra` part named "after..." runs in order as a feed-forward
+    on the stream (it adds to it by itself).  Norms, scales and sums are 32-bit."""
+
+    def _sublayer(self, x, norm, scale, run) -> None:
+        h = ops.cast_rows(x, norm.rt.dtype)
+        y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        run(h, y)
+        norm.add_normed(x, y, scale.weight if scale is not None else None)
+
+    def forward(self, x, step, memory) -> None:
+        if x.is_cuda:
+            ops.settle(x)             # nothing here defers into the stream; what a layer before left is added first
+        self._sublayer(x, self.mixer_norm, self.extra.get("mixer_scale"), lambda h, y: self.mixer.forward(h, y, step, memory))
+        if self.ffn is not None:
+            self._sublayer(x, self.ffn_norm, self.extra.get("ffn_scale"), lambda h, y: self.ffn.forward(h, y, step))
+        for name, part in self.extra.items():
+            if name.startswith("after"):
+                part.forward(ops.cast_rows(x, part.rt.dtype), x, step)

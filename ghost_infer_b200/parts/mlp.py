@@ -9,7 +9,8 @@ keys "gate", "up", "down".
 The same layer with another activation in place of silu (`params["activation"]`: "silu", the default, or
 "gelu_tanh", 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))) is registered as "gated_mlp".
 
-"mlp": the ungated layer residual += Wdown act(Wup h + b_up) + b_down, with `activation` "relu2" (relu(z)^2) and, with
+"mlp": the ungated layer residual += Wdown act(Wup h + b_up) + b_down, with `activation` "relu2" (relu(z)^2) or "gelu"
+(0.5 z (1 + erf(z / sqrt 2)), without biases) and, with
 `bias` (the default), a bias on both products.  Tensor names: prefix + "mlp.{up,down}" and the same + ".b" for the biases,
 unless `params["tensor_names"]` gives others for the keys "up", "up_bias", "down", "down_bias".
 """
@@ -78,8 +79,10 @@ class Mlp(FeedForward):
         self.inter = int(params["intermediate_size"])
         self.activation = str(params.get("activation", "relu2"))
         self.bias = bool(params.get("bias", True))
-        if self.activation != "relu2":
-            raise ValueError(f"unknown activation \"{self.activation}\" (relu2)")
+        if self.activation not in ("relu2", "gelu"):
+            raise ValueError(f"unknown activation \"{self.activation}\" (relu2, gelu)")
+        if self.activation == "gelu" and self.bias:
+            raise ValueError("the gelu layer has no biases")
         d = {"up": "mlp.up", "up_bias": "mlp.up.b", "down": "mlp.down", "down_bias": "mlp.down.b"}
         self.names = {k: self.tensor_name(k, v) for k, v in d.items()}
 
@@ -101,6 +104,11 @@ class Mlp(FeedForward):
             self.b_up, self.b_down = bu, bd
 
     def forward(self, h, residual, step) -> None:
+        if self.activation == "gelu":           # the exact (erf) form, as a step of its own between the two products
+            with ops.bucket("ffn matmul"):
+                act = ops.gelu_rows(linear(h, self.w_up, out_dtype=self.rt.dtype))
+                linear(act, self.w_down, out=residual, accumulate=True)
+            return
         with ops.bucket("ffn matmul"):
             if self.bias:
                 ops.settle(residual)         # the rows get the output's bias from a plain kernel, which adds no partial sums

@@ -34,10 +34,43 @@ class RmsNorm(Norm):
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
         self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
+        self._weight32 = None
+
+    @property
+    def weight32(self) -> torch.Tensor:
+        """The weight as 32-bit values (what joins the residual sum is 32-bit), made when first asked for."""
+        if self._weight32 is None:
+            self._weight32 = self.weight.to(torch.float32).contiguous()
+        return self._weight32
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         with ops.bucket("norm"):
             return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)
+
+
+    def add_normed(self, x: torch.Tensor, y: torch.Tensor, scale: Optional[torch.Tensor] = None) -> None:
+        """x += y / sqrt(mean(y^2) + eps) * w [* scale]: the norm on a sublayer's output, joined to the stream in one pass."""
+        with ops.bucket("norm"):
+            ops.postnorm_add(x, y, self.weight32, self.eps, scale)
+
+
+@register("norm", "channel_scale")
+class ChannelScale(Norm):
+    """A learned number per channel that multiplies a sublayer's normed output (kept 32-bit: it joins the residual sum)."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.size = int(params["size"])
+
+    def weights(self) -> List[WeightSpec]:
+        return [WeightSpec(self.tensor_name("weight", "weight"), (self.size,), "ones")]
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.weight = tensors[self.tensor_name("weight", "weight")].to(device=rt.device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, rows=None, out_dtype=None):
+        raise NotImplementedError("a channel scale is applied by the block that holds it")
 
 
 @register("norm", "layernorm")
