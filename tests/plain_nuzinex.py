@@ -257,3 +257,76 @@ def forward(cfg, weights, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return rms_norm(x, weights["final.norm"], eps) @ weights["head"].T
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# random models
+def random_weights(cfg, seed=0, dtype=np.float64):
+    """Weights for `cfg`, rounded to bfloat16 values so that a bfloat16 file holds them exactly."""
+    rng = np.random.default_rng(seed)
+    d, out = int(cfg["width"]), {}
+
+    def put(name, shape, std=None, mean=0.0):
+        std = std if std is not None else 1.0 / math.sqrt(shape[-1]) if len(shape) > 1 else 0.5
+        a = (rng.standard_normal(shape) * std + mean).astype(np.float32)
+        u = a.view(np.uint32).astype(np.uint64)
+        r = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32)
+        out[name] = r.view(np.float32).astype(dtype).reshape(shape)
+
+    def softmax_tensors(p, m, biased, gated, own_kv=True):
+        H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        put(p + "q", (H * dk, d)); put(p + "q.norm", (H * dk,), 0.2, 1.3); put(p + "o", (d, H * dv))
+        if biased:
+            put(p + "q.b", (H * dk,), 0.3)
+        if gated:
+            put(p + "g", (H * dv, d))
+        if own_kv:
+            put(p + "k", (G * dk, d)); put(p + "v", (G * dv, d)); put(p + "k.norm", (G * dk,), 0.2, 1.3)
+            if biased:
+                put(p + "k.b", (G * dk,), 0.3); put(p + "v.b", (G * dv,), 0.3)
+
+    put("embed", (int(cfg["vocab"]), d), 1.0)
+    put("side.embed", (int(cfg["vocab"]), int(cfg["token_side"]["dim"]) * len(cfg["layers"])), 1.0)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        put(p + "norm1", (d,), 0.1, 1.0); put(p + "ls1", (d,), 0.1, 0.5)
+        if layer["type"] == "attention":
+            softmax_tensors(p + "mix.", m, True, False, m.get("kv_from") is None)
+        elif layer["type"] == "parallel":
+            softmax_tensors(p + "mix.left.", m["left"], False, True)
+            r, q = m["right"], p + "mix.right."
+            H, G, dk, dv, taps = int(r["heads"]), int(r["kv_heads"]), int(r["dim"]), int(r["vdim"]), int(r["conv"])
+            put(q + "q", (G * dk, d)); put(q + "q.conv", (G * dk, taps), 0.6); put(q + "k", (G * dk, d)); put(q + "k.conv", (G * dk, taps), 0.6)
+            put(q + "v", (H * dv, d)); put(q + "v.conv", (H * dv, taps), 0.6); put(q + "b", (H, d)); put(q + "a", (H, d))
+            put(q + "A_log", (H,), 0.5, -0.5); put(q + "dt_bias", (H,), 0.5, -1.0); put(q + "norm", (dv,), 0.1, 1.0)
+            put(q + "g", (H * dv, d)); put(q + "o", (d, H * dv))
+        else:
+            H, dk, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+            put(p + "mix.q", (H * dk, d)); put(p + "mix.k", (H * dk, d)); put(p + "mix.v", (H * dv, d)); put(p + "mix.g", (H * dv, d))
+            put(p + "mix.o", (d, H * dv)); put(p + "mix.norm", (H * dv,), 0.1, 1.0)
+        if layer.get("mlp"):
+            f = int(layer["mlp"]["ff"])
+            put(p + "norm2", (d,), 0.1, 1.0); put(p + "ls2", (d,), 0.1, 0.5)
+            put(p + "mlp.up", (f, d)); put(p + "mlp.down", (d, f))
+        sd = int(cfg["token_side"]["dim"])
+        put(p + "side.gate", (sd, d)); put(p + "side.proj", (d, sd)); put(p + "side.norm", (d,), 0.05, 0.3)
+    put("final.norm", (d,), 0.1, 1.0)
+    put("head", (int(cfg["vocab"]), d))
+    return out
+
+
+def write_safetensors_bf16(path, tensors):
+    """Writes float arrays as bfloat16 (the values must be bfloat16 values already) in the safetensors layout."""
+    header, blobs, at = {}, [], 0
+    for name, a in tensors.items():
+        raw = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> 16).astype("<u2").tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(a.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for b in blobs:
+            f.write(b)
