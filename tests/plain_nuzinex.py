@@ -261,6 +261,14 @@ def forward(cfg, weights, tokens, layers_out=None):
 
 # ---------------------------------------------------------------------------------------------------------------
 # random models
+def bf16_values(a, dtype=np.float64):
+    """`a` rounded (to nearest, ties to even) to values a bfloat16 holds."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    r = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32)
+    return r.view(np.float32).astype(dtype).reshape(a.shape)
+
+
 def random_weights(cfg, seed=0, dtype=np.float64):
     """Weights for `cfg`, rounded to bfloat16 values so that a bfloat16 file holds them exactly."""
     rng = np.random.default_rng(seed)
@@ -268,10 +276,7 @@ def random_weights(cfg, seed=0, dtype=np.float64):
 
     def put(name, shape, std=None, mean=0.0):
         std = std if std is not None else 1.0 / math.sqrt(shape[-1]) if len(shape) > 1 else 0.5
-        a = (rng.standard_normal(shape) * std + mean).astype(np.float32)
-        u = a.view(np.uint32).astype(np.uint64)
-        r = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32)
-        out[name] = r.view(np.float32).astype(dtype).reshape(shape)
+        out[name] = bf16_values(rng.standard_normal(shape) * std + mean, dtype)
 
     def softmax_tensors(p, m, biased, gated, own_kv=True):
         H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
