@@ -162,9 +162,51 @@ LATENT_SIZES = {
 }
 
 
+def _nuzinex(width, heads, kv, dim, vdim, window, ff, left_heads, left_kv, left_dim, delta_heads, delta_qk, delta_dim, delta_vdim,
+             conv, lin_heads, lin_dim, lin_vdim, side, vocab, **_):
+    own = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window},
+           "rot": {"base": 10000.0, "dims": dim}}
+    left = {"heads": left_heads, "kv_heads": left_kv, "dim": left_dim, "vdim": left_dim, "scale": left_dim ** -0.5,
+            "rot": {"base": 1000000.0, "dims": left_dim // 2}}
+    right = {"heads": delta_heads, "kv_heads": delta_qk, "dim": delta_dim, "vdim": delta_vdim, "conv": conv}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "attention", "mixer": own, "mlp": mlp},
+              {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp},
+              {"type": "lightning", "mixer": {"heads": lin_heads, "dim": lin_dim, "vdim": lin_vdim,
+                                              "decay": [1.0 - 2.0 ** -(1 + 7 * h / max(1, lin_heads - 1)) for h in range(lin_heads)]}, "mlp": mlp},
+              {"type": "attention", "mixer": dict(own, kv_from=0), "mlp": mlp}]
+    return {"architecture": "Nuzinex", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "token_side": {"dim": side}, "layers": layers}
+
+
+# layer sizes of the kind real models have: windowed attention, attention beside a delta rule, linear attention, and a
+# layer that reads the first one's keys and values, each with a dense feed-forward.  Beside it the hybrid decoder with
+# windowed attention and state-space layers (`_barovik`; its routed experts sized to the same feed-forward width per token)
+NUZINEX_SIZES = {
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, vdim=64, window=1024, ff=8192, left_heads=16, left_kv=4, left_dim=128,
+                  delta_heads=16, delta_qk=8, delta_dim=128, delta_vdim=128, conv=4, lin_heads=16, lin_dim=128, lin_vdim=128, side=256,
+                  vocab=32000, chunk=1024, ssm_heads=64, ssm_dim=64, state=128, groups=8, experts=16, top=2, expert_ff=2048,
+                  shared_ff=4096, pairs=2),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, window=2048, ff=14336, left_heads=32, left_kv=8, left_dim=128,
+                  delta_heads=32, delta_qk=16, delta_dim=128, delta_vdim=128, conv=4, lin_heads=32, lin_dim=128, lin_vdim=128, side=256,
+                  vocab=32000, chunk=2048, ssm_heads=128, ssm_dim=64, state=128, groups=8, experts=16, top=2, expert_ff=4096,
+                  shared_ff=6144, pairs=2),
+    "w2048_odd": dict(width=2048, heads=24, kv=4, dim=64, vdim=40, window=500, ff=6144, left_heads=12, left_kv=12, left_dim=64,
+                      delta_heads=12, delta_qk=12, delta_dim=96, delta_vdim=64, conv=3, lin_heads=32, lin_dim=64, lin_vdim=64, side=96,
+                      vocab=32000, chunk=500, ssm_heads=64, ssm_dim=40, state=96, groups=4, experts=32, top=4, expert_ff=1024,
+                      shared_ff=2048, pairs=2),
+}
+
+
+def _barovik_beside(z):
+    keys = ("width", "heads", "kv", "dim", "vdim", "chunk", "ff", "ssm_heads", "ssm_dim", "state", "groups", "experts", "top",
+            "expert_ff", "shared_ff", "vocab", "pairs")
+    return _barovik(**{k: z[k] for k in keys})
+
+
 def measure_hybrid(args):
-    """`--workload barovik` / `--workload navalorn`: prompt and decode throughput of that decoder at a few real layer sizes
-    (random weights), beside the Llama decoder with the same width, heads, feed-forward width and number of layers; and the
+    """`--workload barovik` / `--workload navalorn` / `--workload nuzinex`: prompt and decode throughput of that decoder at a few real layer sizes
+    (random weights), beside the Llama decoder with the same width, heads, feed-forward width and number of layers (nuzinex:
+    beside the hybrid decoder with windowed attention and state-space layers, and the Llama decoder); and the
     device time per kind of operation for one prompt step and one decode step of each.  One JSON line."""
     import gc
     import numpy as np
@@ -245,11 +287,15 @@ def measure_hybrid(args):
 
     latent = args.workload == "navalorn"
     sizes, build, label = (LATENT_SIZES, _navalorn, "navalorn") if latent else (HYBRID_SIZES, _barovik, "barovik")
+    if args.workload == "nuzinex":
+        sizes, build, label = NUZINEX_SIZES, _nuzinex, "nuzinex"
     names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     for name in names:
         z = sizes[name]
         hybrid = one(build(**z))
         out[name] = {"sizes": z, label: hybrid}
+        if label == "nuzinex" and not args.skip_points:
+            out[name]["barovik_equal_size"] = one(_barovik_beside(z))
         if not args.skip_points:
             out[name]["llama_equal_size"] = one(_llama_like(z["width"], z["heads"], z["kv"], z["llama_dim"] if latent else z["dim"], z["ff"],
                                                             z["vocab"], 2 * z["pairs"]))
@@ -394,10 +440,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik", "navalorn"],
-                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik, navalorn: the hybrid decoder, or the "
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik", "navalorn", "nuzinex"],
+                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik, navalorn, nuzinex: the hybrid decoder, or the "
                          "decoder with a latent cache, beside the Llama decoder at equal layer sizes (--sizes, --batch, --held)")
-    ap.add_argument("--sizes", default="", help="for --workload barovik / navalorn: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--sizes", default="", help="for --workload barovik / navalorn / nuzinex: which of its sizes to run, with commas (default: all)")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
@@ -420,7 +466,7 @@ def main():
         for kv in filter(None, args.tune.split(",")):
             k, v = kv.split("=")
             _ops.TUNE[k] = type(_ops.TUNE[k])(float(v))
-    if args.workload in ("barovik", "navalorn"):
+    if args.workload in ("barovik", "navalorn", "nuzinex"):
         return measure_hybrid(args)
     if args.workload != "8b":
         return run_workload(args.workload, args)
