@@ -11,10 +11,18 @@
 // Everything after the loads is 32-bit.  The tokens of a sequence are walked in order whatever the step holds, so a prompt
 // cut anywhere, alone or in a batch, gives the same bits.
 //
-// Work split: grid (heads, sequences, tiles of 32 columns of S).  A column of S (K numbers) belongs to 8 neighbouring lanes,
-// lane l holding rows l, l + 8, ...; a column's two dot products end with three exchanges among its lanes.  Tokens go
-// through shared memory 16 at a time.  State per slot: [heads][V][K] floats (a column's rows side by side) at the start of
-// the slot's row; slot -1 (a padding row of a fixed-size launch) uses the last row of the matrix.
+// Work split: grid (heads, sequences, tiles of 32, 16 or 8 columns of S; the widest tile that still gives every SM a
+// block is chosen by the launcher).  A column of S (K numbers) belongs to 8 neighbouring lanes; lane l holds rows
+// 4 (l + 8 m) .. + 3 for m = 0, 1, ..., so a column's rows are read from the state, and a token's key and query from shared
+// memory, sixteen bytes at a time.  The delta rule's S^T k ends with three exchanges among a column's lanes, token by
+// token, since the next write depends on it; the read-outs S^T q of eight tokens are exchanged together (seven exchanges
+// instead of twenty-four).  The order of every sum follows from K alone: one token or a thousand, alone or in a batch,
+// whatever the tile, give the same bits.
+// Four more warps of the block prepare the next tokens while these work: they load a chunk's rows, apply silu, unit norms,
+// the decay and the write strength (one warp per token), and write the previous chunk's read-outs to memory in whole
+// lines.  Two buffers in shared memory, one barrier per chunk.
+// State per slot: [heads][V][K] floats (a column's rows side by side) at the start of the slot's row; slot -1 (a padding row
+// of a fixed-size launch) uses the last row of the matrix.
 #include <math.h>
 
 #include "api.h"
@@ -22,124 +30,251 @@
 
 namespace {
 
-constexpr int LS_COLS = 32, LS_LANES = 8, LS_CH = 16;
+constexpr int LS_LANES = 8;        // lanes of a column
+constexpr int LS_PREP = 128;       // threads that prepare tokens and write read-outs
+constexpr int LS_TB = 8;           // read-outs exchanged together
 
 __device__ __forceinline__ float ls_silu(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float ls_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-template <typename T, int KR>
-__global__ void __launch_bounds__(LS_COLS * LS_LANES)
-linear_state_kernel(float* __restrict__ o, const T* q, long ldq, const T* k, long ldk, const T* v, long ldv, const T* a_in,
-                    long lda, const T* b_in, long ldb, const float* __restrict__ decay_c, const float* __restrict__ dt_bias,
-                    float* state, long state_ld, int state_rows, const int* __restrict__ cu_seqlens,
-                    const int* __restrict__ seq_slots, int heads, int qk_heads, int K, int V, int in_act, int unit_norm,
-                    float norm_eps, float q_scale, int delta) {
-  constexpr int Kp = KR * LS_LANES;
-  constexpr int NT = LS_COLS * LS_LANES;
-  extern __shared__ __align__(16) float sm[];
-  float* sq = sm;                      // [LS_CH][Kp]
-  float* sk = sq + LS_CH * Kp;         // [LS_CH][Kp]
-  float* sv = sk + LS_CH * Kp;         // [LS_CH][LS_COLS]
-  float* sg = sv + LS_CH * LS_COLS;    // [LS_CH]
-  float* sb = sg + LS_CH;              // [LS_CH]
-  gi::pdl_prologue();
-  const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * LS_COLS;
-  const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
-  if (qlen <= 0) return;
-  const int slot = seq_slots[b];
-  float* S_row = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + (size_t)h * V * K;
-  const int hk = h / (heads / qk_heads);
-  const int tid = threadIdx.x, col = tid / LS_LANES, lane = tid % LS_LANES;
-  const int j = j0 + col;
-  float S[KR];
+// One halving step among a column's 8 lanes: of 2 * HALF values a lane keeps the half its bit `BIT` of the lane number
+// names and adds the other lane's partial sums of the same values.
+template <int HALF, int BIT>
+__device__ __forceinline__ void ls_halve(float (&v)[LS_TB], int lane) {
+  const bool upper = (lane & BIT) != 0;
 #pragma unroll
-  for (int r = 0; r < KR; ++r) {
-    const int i = lane + LS_LANES * r;
-    S[r] = (j < V && i < K) ? S_row[(size_t)j * K + i] : 0.f;
+  for (int k = 0; k < HALF; ++k) {
+    const float send = upper ? v[k] : v[k + HALF];
+    const float keep = upper ? v[k + HALF] : v[k];
+    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, BIT);
   }
-  const float dc = decay_c[h];
-  const float rate = a_in != nullptr ? expf(dc) : 0.f, bias = (a_in != nullptr && dt_bias != nullptr) ? dt_bias[h] : 0.f;
-  for (int c0 = 0; c0 < qlen; c0 += LS_CH) {
-    const int n = min(LS_CH, qlen - c0);
-    const size_t tok = (size_t)tok0 + c0;
-    __syncthreads();                   // the chunk before has been used up
-    for (int idx = tid; idx < n * Kp; idx += NT) {
-      const int t = idx / Kp, i = idx % Kp;
-      float qv = 0.f, kv = 0.f;
-      if (i < K) {
-        qv = gi::ldf(q + (tok + t) * ldq + (size_t)hk * K + i);
-        kv = gi::ldf(k + (tok + t) * ldk + (size_t)hk * K + i);
-        if (in_act) { qv = ls_silu(qv); kv = ls_silu(kv); }
-      }
-      sq[idx] = qv;
-      sk[idx] = kv;
-    }
-    for (int idx = tid; idx < n * LS_COLS; idx += NT) {
-      const int t = idx / LS_COLS, c = idx % LS_COLS;
-      float vv = 0.f;
-      if (j0 + c < V) {
-        vv = gi::ldf(v + (tok + t) * ldv + (size_t)h * V + j0 + c);
-        if (in_act) vv = ls_silu(vv);
-      }
-      sv[idx] = vv;
-    }
-    if (tid < n) {
-      sg[tid] = a_in != nullptr ? expf(-rate * ls_softplus(gi::ldf(a_in + (tok + tid) * lda + h) + bias)) : dc;
-      sb[tid] = b_in != nullptr ? 1.0f / (1.0f + expf(-gi::ldf(b_in + (tok + tid) * ldb + h))) : 1.0f;
-    }
-    __syncthreads();
-    if (unit_norm) {
-      const int warp = tid >> 5, wl = tid & 31;
-      for (int t = warp; t < n; t += NT / 32) {
-        float s1 = 0.f, s2 = 0.f;
-        for (int i = wl; i < Kp; i += 32) {
-          s1 = fmaf(sq[t * Kp + i], sq[t * Kp + i], s1);
-          s2 = fmaf(sk[t * Kp + i], sk[t * Kp + i], s2);
+}
+
+struct LsArgs {
+  float* o;
+  const void *q, *k, *v, *a_in, *b_in;
+  long ldq, ldk, ldv, lda, ldb;
+  const float *decay_c, *dt_bias;
+  float* state;
+  long state_ld;
+  int state_rows;
+  const int *cu_seqlens, *seq_slots;
+  int heads, qk_heads, K, V, in_act, unit_norm, vec_state;
+  float norm_eps, q_scale;
+};
+
+// tokens per chunk: two buffers of it stay under 48 KB of shared memory
+template <int KR> struct LsChunk { static constexpr int value = KR >= 32 ? 8 : 16; };
+
+template <typename T, int KR, int COLS, bool DELTA>
+__global__ void __launch_bounds__(COLS * LS_LANES + LS_PREP)
+linear_state_kernel(const LsArgs a) {
+  constexpr int Kp = KR * LS_LANES;            // rows with padding
+  constexpr int M = KR / 4;                    // groups of four rows per lane; also a preparing lane's share of a row
+  constexpr int NC = COLS * LS_LANES;          // threads that hold S
+  constexpr int CH = LsChunk<KR>::value;
+  constexpr int BUF = 2 * CH * Kp + 2 * CH * COLS + 2 * CH;
+  extern __shared__ __align__(16) float sm[];
+  gi::pdl_prologue();
+  const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * COLS;
+  const int tok0 = a.cu_seqlens[b], qlen = a.cu_seqlens[b + 1] - tok0;
+  if (qlen <= 0) return;
+  const int K = a.K, V = a.V;
+  const int slot = a.seq_slots[b];
+  float* S_row = a.state + (size_t)(slot >= 0 ? slot : a.state_rows - 1) * a.state_ld + (size_t)h * V * K;
+  const int hk = h / (a.heads / a.qk_heads);
+  const int tid = threadIdx.x;
+  const bool prep = tid >= NC;
+  const int n_chunks = (qlen + CH - 1) / CH;
+  const size_t o_ld = (size_t)a.heads * V;
+  const T* qp = (const T*)a.q; const T* kp = (const T*)a.k; const T* vp = (const T*)a.v;
+  const T* ap = (const T*)a.a_in; const T* bp = (const T*)a.b_in;
+  const float dc = a.decay_c[h];
+  const float rate = ap != nullptr ? expf(dc) : 0.f, bias = (ap != nullptr && a.dt_bias != nullptr) ? a.dt_bias[h] : 0.f;
+
+  // a chunk's tokens made ready in buffer `buf`: one warp per token
+  auto prepare = [&](int c, float* buf) {
+    float* sq = buf; float* sk = sq + CH * Kp; float* sv = sk + CH * Kp; float* sg = sv + CH * COLS; float* sb = sg + CH;
+    const int n = min(CH, qlen - c * CH);
+    const int pw = (tid - NC) >> 5, pl = tid & 31;
+    for (int t = pw; t < n; t += LS_PREP / 32) {
+      const size_t tok = (size_t)tok0 + (size_t)c * CH + t;
+      float qv[M], kv[M];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < M; ++i) {
+        const int r = pl + 32 * i;
+        qv[i] = 0.f; kv[i] = 0.f;
+        if (r < K) {
+          qv[i] = gi::ldf(qp + tok * a.ldq + (size_t)hk * K + r);
+          kv[i] = gi::ldf(kp + tok * a.ldk + (size_t)hk * K + r);
+          if (a.in_act) { qv[i] = ls_silu(qv[i]); kv[i] = ls_silu(kv[i]); }
         }
+        s1 = fmaf(qv[i], qv[i], s1);
+        s2 = fmaf(kv[i], kv[i], s2);
+      }
+      float fq = 1.f, fk = 1.f;
+      if (a.unit_norm) {
         s1 = gi::warp_sum(s1);
         s2 = gi::warp_sum(s2);
-        const float fq = q_scale / sqrtf(s1 + norm_eps), fk = 1.0f / sqrtf(s2 + norm_eps);
-        for (int i = wl; i < Kp; i += 32) {
-          sq[t * Kp + i] *= fq;
-          sk[t * Kp + i] *= fk;
+        fq = a.q_scale / sqrtf(s1 + a.norm_eps);
+        fk = 1.0f / sqrtf(s2 + a.norm_eps);
+      }
+#pragma unroll
+      for (int i = 0; i < M; ++i) {
+        sq[t * Kp + pl + 32 * i] = qv[i] * fq;
+        sk[t * Kp + pl + 32 * i] = kv[i] * fk;
+      }
+      for (int cc = pl; cc < COLS; cc += 32) {
+        float vv = 0.f;
+        if (j0 + cc < V) {
+          vv = gi::ldf(vp + tok * a.ldv + (size_t)h * V + j0 + cc);
+          if (a.in_act) vv = ls_silu(vv);
+        }
+        sv[t * COLS + cc] = vv;
+      }
+      if (pl == 0) {
+        sg[t] = ap != nullptr ? expf(-rate * ls_softplus(gi::ldf(ap + tok * a.lda + h) + bias)) : dc;
+        sb[t] = bp != nullptr ? 1.0f / (1.0f + expf(-gi::ldf(bp + tok * a.ldb + h))) : 1.0f;
+      }
+    }
+  };
+  // a chunk's read-outs from buffer `buf` to memory, by the threads [first, first + count)
+  auto write_out = [&](int c, const float* buf, int first, int count) {
+    const float* so = buf + 2 * CH * Kp + CH * COLS + 2 * CH;
+    const int n = min(CH, qlen - c * CH);
+    for (int idx = tid - first; idx < n * COLS; idx += count) {
+      const int t = idx / COLS, cc = idx % COLS;
+      if (j0 + cc < V) a.o[((size_t)tok0 + (size_t)c * CH + t) * o_ld + (size_t)h * V + j0 + cc] = so[idx];
+    }
+  };
+
+  const int col = tid / LS_LANES, lane = tid % LS_LANES;    // of the threads that hold S
+  const int j = j0 + col;
+  float S[KR];
+  if (prep) {
+    prepare(0, sm);
+  } else {
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const int i = 4 * (lane + LS_LANES * m);
+      if (a.vec_state && j < V && i < K) {
+        const float4 s4 = *reinterpret_cast<const float4*>(S_row + (size_t)j * K + i);
+        S[4 * m] = s4.x; S[4 * m + 1] = s4.y; S[4 * m + 2] = s4.z; S[4 * m + 3] = s4.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[4 * m + e] = (j < V && i + e < K) ? S_row[(size_t)j * K + i + e] : 0.f;
+      }
+    }
+  }
+  for (int c = 0; c < n_chunks; ++c) {
+    __syncthreads();             // chunk c is ready in buffer c & 1; the other buffer's tokens and this one's read-outs are used up
+    float* buf = sm + (c & 1) * BUF;
+    if (prep) {
+      if (c > 0) write_out(c - 1, sm + ((c - 1) & 1) * BUF, NC, LS_PREP);
+      if (c + 1 < n_chunks) prepare(c + 1, sm + ((c + 1) & 1) * BUF);
+      continue;
+    }
+    const float* sq = buf; const float* sk = sq + CH * Kp; const float* sv = sk + CH * Kp;
+    const float* sg = sv + CH * COLS; const float* sb = sg + CH;
+    float* so = buf + 2 * CH * Kp + CH * COLS + 2 * CH;
+    const int n = min(CH, qlen - c * CH);
+    for (int t0 = 0; t0 < n; t0 += LS_TB) {
+      float acc[LS_TB];
+#pragma unroll
+      for (int tl = 0; tl < LS_TB; ++tl) {
+        const int t = t0 + tl;
+        acc[tl] = 0.f;
+        if (t < n) {             // the same for the whole block
+          const float g = sg[t];
+          float kk[KR], qq[KR];
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const float4 k4 = *reinterpret_cast<const float4*>(sk + t * Kp + 4 * (lane + LS_LANES * m));
+            const float4 q4 = *reinterpret_cast<const float4*>(sq + t * Kp + 4 * (lane + LS_LANES * m));
+            kk[4 * m] = k4.x; kk[4 * m + 1] = k4.y; kk[4 * m + 2] = k4.z; kk[4 * m + 3] = k4.w;
+            qq[4 * m] = q4.x; qq[4 * m + 1] = q4.y; qq[4 * m + 2] = q4.z; qq[4 * m + 3] = q4.w;
+          }
+          float u = sv[t * COLS + col];
+          if (DELTA) {
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;     // four chains, then a tree: the order is fixed by K alone
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              d0 = fmaf(S[4 * m], kk[4 * m], d0);
+              d1 = fmaf(S[4 * m + 1], kk[4 * m + 1], d1);
+              d2 = fmaf(S[4 * m + 2], kk[4 * m + 2], d2);
+              d3 = fmaf(S[4 * m + 3], kk[4 * m + 3], d3);
+            }
+            float d = (d0 + d1) + (d2 + d3);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            u = sb[t] * (u - g * d);
+          }
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            S[4 * m] = fmaf(kk[4 * m], u, g * S[4 * m]);
+            S[4 * m + 1] = fmaf(kk[4 * m + 1], u, g * S[4 * m + 1]);
+            S[4 * m + 2] = fmaf(kk[4 * m + 2], u, g * S[4 * m + 2]);
+            S[4 * m + 3] = fmaf(kk[4 * m + 3], u, g * S[4 * m + 3]);
+            a0 = fmaf(S[4 * m], qq[4 * m], a0);
+            a1 = fmaf(S[4 * m + 1], qq[4 * m + 1], a1);
+            a2 = fmaf(S[4 * m + 2], qq[4 * m + 2], a2);
+            a3 = fmaf(S[4 * m + 3], qq[4 * m + 3], a3);
+          }
+          acc[tl] = (a0 + a1) + (a2 + a3);
         }
       }
-      __syncthreads();
-    }
-    for (int t = 0; t < n; ++t) {
-      const float g = sg[t];
-      float kk[KR];
-#pragma unroll
-      for (int r = 0; r < KR; ++r) kk[r] = sk[t * Kp + lane + LS_LANES * r];
-      float u = sv[t * LS_COLS + col];
-      if (delta) {
-        float d = 0.f;
-#pragma unroll
-        for (int r = 0; r < KR; ++r) d = fmaf(S[r], kk[r], d);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        u = sb[t] * (u - g * d);
-      }
-      float acc = 0.f;
-#pragma unroll
-      for (int r = 0; r < KR; ++r) {
-        S[r] = fmaf(kk[r], u, g * S[r]);
-        acc = fmaf(S[r], sq[t * Kp + lane + LS_LANES * r], acc);
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (lane == 0 && j < V) o[(tok + t) * ((size_t)heads * V) + (size_t)h * V + j] = acc;
+      ls_halve<4, 4>(acc, lane);
+      ls_halve<2, 2>(acc, lane);
+      ls_halve<1, 1>(acc, lane);
+      // lane l of a column now holds token t0 + l
+      if (t0 + lane < n) so[(t0 + lane) * COLS + col] = acc[0];
     }
   }
-  if (j < V) {
+  __syncthreads();
+  write_out(n_chunks - 1, sm + ((n_chunks - 1) & 1) * BUF, 0, NC + LS_PREP);
+  if (!prep && j < V) {
 #pragma unroll
-    for (int r = 0; r < KR; ++r) {
-      const int i = lane + LS_LANES * r;
-      if (i < K) S_row[(size_t)j * K + i] = S[r];
+    for (int m = 0; m < M; ++m) {
+      const int i = 4 * (lane + LS_LANES * m);
+      if (a.vec_state && i < K) {
+        *reinterpret_cast<float4*>(S_row + (size_t)j * K + i) = make_float4(S[4 * m], S[4 * m + 1], S[4 * m + 2], S[4 * m + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (i + e < K) S_row[(size_t)j * K + i + e] = S[4 * m + e];
+      }
     }
   }
+}
+
+int ls_sm_count() {
+  static int n[gi::MAX_DEVICES_SEEN] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= gi::MAX_DEVICES_SEEN) return 148;
+  if (n[dev] == 0 && cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n[dev] = 148;
+  return n[dev];
+}
+
+template <typename T, int KR, int COLS>
+cudaError_t ls_launch(const LsArgs& a, int n_seqs, bool delta, cudaStream_t stream) {
+  constexpr int CH = LsChunk<KR>::value;
+  const size_t smem = 2 * (size_t)(2 * CH * KR * LS_LANES + 2 * CH * COLS + 2 * CH) * sizeof(float);
+  const dim3 grid(a.heads, n_seqs, (a.V + COLS - 1) / COLS), block(COLS * LS_LANES + LS_PREP);
+  return delta ? gi::launch(linear_state_kernel<T, KR, COLS, true>, grid, block, smem, stream, a)
+               : gi::launch(linear_state_kernel<T, KR, COLS, false>, grid, block, smem, stream, a);
+}
+
+template <typename T, int KR>
+cudaError_t ls_pick_tile(const LsArgs& a, int n_seqs, bool delta, cudaStream_t stream) {
+  // the widest tile that still gives every SM a block: with fewer blocks than SMs the token-by-token walk, whose length a
+  // block cannot shorten, runs on a part of the device only
+  const long per = (long)a.heads * n_seqs, sms = ls_sm_count();
+  if (per * ((a.V + 31) / 32) >= sms || a.V <= 8) return ls_launch<T, KR, 32>(a, n_seqs, delta, stream);
+  if (per * ((a.V + 15) / 16) >= sms) return ls_launch<T, KR, 16>(a, n_seqs, delta, stream);
+  return ls_launch<T, KR, 8>(a, n_seqs, delta, stream);
 }
 
 }  // namespace
@@ -156,21 +291,21 @@ extern "C" int gi_linear_state(float* o, const void* q, long ldq, const void* k,
   if (!o || !q || !k || !v || !decay_c || !state || !cu_seqlens || !seq_slots) return gi::fail(GI_ERR_ARG, "linear_state: a missing pointer");
   if (delta && b_in == nullptr) return gi::fail(GI_ERR_ARG, "linear_state: the delta rule needs its write strengths");
   if (state_ld < (long)heads * K * V) return gi::fail(GI_ERR_ARG, "linear_state: state rows of %ld floats, wanted %ld", state_ld, (long)heads * K * V);
-  const dim3 grid(heads, n_seqs, (V + LS_COLS - 1) / LS_COLS), block(LS_COLS * LS_LANES);
+  LsArgs a;
+  a.o = o; a.q = q; a.k = k; a.v = v; a.a_in = a_in; a.b_in = b_in;
+  a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.lda = lda; a.ldb = ldb;
+  a.decay_c = decay_c; a.dt_bias = dt_bias; a.state = state; a.state_ld = state_ld; a.state_rows = state_rows;
+  a.cu_seqlens = cu_seqlens; a.seq_slots = seq_slots;
+  a.heads = heads; a.qk_heads = qk_heads; a.K = K; a.V = V; a.in_act = in_act; a.unit_norm = unit_norm;
+  // sixteen bytes of a column at a time where every column of every slot starts on such a boundary
+  a.vec_state = (K % 4 == 0 && state_ld % 4 == 0 && ((size_t)state & 15) == 0) ? 1 : 0;
+  a.norm_eps = norm_eps; a.q_scale = q_scale;
   cudaError_t e = cudaSuccess;
-#define GI_LS_LAUNCH(KR)                                                                                                  \
-  do {                                                                                                                    \
-    const size_t smem = (size_t)(2 * LS_CH * (KR) * LS_LANES + LS_CH * LS_COLS + 2 * LS_CH) * sizeof(float);              \
-    e = gi::launch(linear_state_kernel<T, KR>, grid, block, smem, (cudaStream_t)stream, o, (const T*)q, ldq, (const T*)k, \
-                   ldk, (const T*)v, ldv, (const T*)a_in, lda, (const T*)b_in, ldb, decay_c, dt_bias, state, state_ld,   \
-                   state_rows, cu_seqlens, seq_slots, heads, qk_heads, K, V, in_act, unit_norm, norm_eps, q_scale, delta); \
-  } while (0)
   GI_DISPATCH_DTYPE(dtype, T, {
-    if (K <= 4 * LS_LANES) GI_LS_LAUNCH(4);
-    else if (K <= 8 * LS_LANES) GI_LS_LAUNCH(8);
-    else if (K <= 16 * LS_LANES) GI_LS_LAUNCH(16);
-    else GI_LS_LAUNCH(32);
+    if (K <= 4 * LS_LANES) e = ls_pick_tile<T, 4>(a, n_seqs, delta != 0, (cudaStream_t)stream);
+    else if (K <= 8 * LS_LANES) e = ls_pick_tile<T, 8>(a, n_seqs, delta != 0, (cudaStream_t)stream);
+    else if (K <= 16 * LS_LANES) e = ls_pick_tile<T, 16>(a, n_seqs, delta != 0, (cudaStream_t)stream);
+    else e = ls_pick_tile<T, 32>(a, n_seqs, delta != 0, (cudaStream_t)stream);
   });
-#undef GI_LS_LAUNCH
   return gi::check(e, "linear_state");
 }

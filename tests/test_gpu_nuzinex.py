@@ -121,8 +121,8 @@ def toks(name, n, seed):
     return np.random.default_rng(seed).integers(0, CONFIGS[name]["vocab"], size=n).tolist()
 
 
-def check(got, ref, dtype, what=""):
-    """32-bit: sums of a few hundred terms over a dozen dependent stages, relative to the largest logit.  bfloat16:
+def check(got, ref, dtype, what="", keep=None):
+    """`keep`: the positions that count (all, if None).  32-bit: sums of a few hundred terms over a dozen dependent stages, relative to the largest logit.  bfloat16:
     activations rounded to 8 bits between kernels; every sublayer's output is normed, so errors do not grow with depth.
     A key one position off, a lost state or a wrong angle moves logits by tens of percent."""
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
@@ -130,6 +130,8 @@ def check(got, ref, dtype, what=""):
     assert np.isfinite(got).all(), f"{what}: non-finite logits"
     scale = max(1.0, float(np.abs(ref).max()))
     err = np.abs(got - ref)
+    if keep is not None:
+        err = err[np.asarray(keep, dtype=bool)]
     if dtype == "float32":
         assert err.max() <= 5e-5 * scale, f"{what}: max error {err.max():.3e} (scale {scale:.2f}) at {np.unravel_index(err.argmax(), err.shape)}"
     else:
@@ -547,6 +549,18 @@ def random_config(seed, sixteen_bit):
     return model_cfg(width, pick([64, 200] if sixteen_bit else [50, 97, 260]), side, layers, eps=float(10 ** r.uniform(-6, -4)))
 
 
+def well_conditioned(cfg, w, tokens, ref):
+    """The positions whose logits the plain implementation itself keeps when its weights and the sums that take their type
+    are 32-bit.  Where a drawn model norms a vector that nearly cancelled (a read-out of a few terms in a sequence's first
+    tokens), rounding alone moves the logits by more than a fault would elsewhere; such a position says nothing about the
+    kernels.  They are few: more than one in twenty-five fails the test."""
+    w32 = {k: (v.astype(np.float32) if v.dtype.kind == "f" else v) for k, v in w.items()}
+    low = np.asarray(pz.forward(cfg, w32, tokens), dtype=np.float64)
+    keep = np.abs(low - ref).max(axis=1) <= 1e-5 * max(1.0, float(np.abs(ref).max()))
+    assert keep.mean() >= 0.96, f"{cfg}: {int((~keep).sum())} of {len(keep)} positions are ill-conditioned"
+    return keep
+
+
 @pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in range(8)] + [(s, "bfloat16") for s in range(100, 105)])
 def test_configurations_drawn_at_random(seed, dtype):
     """Whole prompt, prompt cut in three, the tail token by token, and a batch of three, on a model nobody chose."""
@@ -556,13 +570,14 @@ def test_configurations_drawn_at_random(seed, dtype):
     r = np.random.default_rng(seed + 1)
     prompts = [r.integers(0, cfg["vocab"], size=n).tolist() for n in (150, 70, 9)]
     refs = [pz.forward(cfg, w, p) for p in prompts]
-    check(run_whole(eng, prompts[0]), refs[0], dtype, f"{cfg}: whole")
+    keeps = [well_conditioned(cfg, w, p, ref) for p, ref in zip(prompts, refs)]
+    check(run_whole(eng, prompts[0]), refs[0], dtype, f"{cfg}: whole", keeps[0])
     s = eng.cache.open_slot()
     rows = [eng.step([gi.StepEntry(s, prompts[0][a:b], list(range(b - a)))]).cpu().numpy() for a, b in ((0, 2), (2, 67), (67, 130))]
     run = eng.decoder([s])
     rows += [run.forward(tokens=[t]).cpu().numpy().copy() for t in prompts[0][130:]]
     eng.cache.close_slot(s)
-    check(np.concatenate(rows, 0), refs[0], dtype, f"{cfg}: cut and decoded")
+    check(np.concatenate(rows, 0), refs[0], dtype, f"{cfg}: cut and decoded", keeps[0])
     slots = [eng.cache.open_slot() for _ in prompts]
     cut = [len(p) - 5 for p in prompts]
     out = eng.step([gi.StepEntry(sl, p[:c], list(range(c))) for sl, p, c in zip(slots, prompts, cut)]).cpu().numpy()
@@ -575,7 +590,7 @@ def test_configurations_drawn_at_random(seed, dtype):
     for sl in slots:
         eng.cache.close_slot(sl)
     for i in range(3):
-        check(np.concatenate(got[i], 0), refs[i], dtype, f"{cfg}: request {i} of a batch")
+        check(np.concatenate(got[i], 0), refs[i], dtype, f"{cfg}: request {i} of a batch", keeps[i])
 
 
 # ---- the replay program as a user runs it ----------------------------------------------------------------------------
