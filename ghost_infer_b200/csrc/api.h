@@ -158,6 +158,7 @@ int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, 
 int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                     long ldo, int tile_n, void* stream);
 #define GI_ACT_RELU2 0x200      // or-ed into GI_TC_STORE_BF16 (gi_gemm_tc_bf16_bias): out = relu(A W^T + bias)^2 as bfloat16
+#define GI_ACT_GELU_ERF 0x400   // or-ed into GI_TC_STORE_BF16: out = gelu(A W^T) in the exact (erf) form as bfloat16, no bias
 // gi_gemm_tc_bf16 with `bias` (bfloat16 [N], or null) for the mode GI_TC_STORE_BF16 | GI_ACT_RELU2.
 int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K, long lda,
                          long ldw, long ldo, int tile_n, void* stream);

@@ -45,7 +45,8 @@ struct TilePlan {
   int wide_cols;     // column tiles of full width
   int narrow;        // width of the column tiles after them (0: none)
   int n_tiles;       // all tiles
-  int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form); the bfloat16 store's: 2 relu squared
+  int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form); the bfloat16 store's: 2 relu squared,
+                     // 3 gelu in its exact (erf) form
   const __nv_bfloat16* bias;   // added to the sums before the bfloat16 store's activation (one per output column), or null
 };
 
@@ -322,6 +323,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   v1 = fmaxf(v1, 0.f);
                   v0 *= v0;
                   v1 *= v1;
+                } else if (plan.act == 3) {
+                  // an ungated hidden layer with the exact gelu, on the 32-bit sums
+                  v0 = 0.5f * v0 * (1.0f + erff(v0 * 0.7071067811865476f));
+                  v1 = 0.5f * v1 * (1.0f + erff(v1 * 0.7071067811865476f));
                 }
                 __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
                 p[e] = *reinterpret_cast<uint32_t*>(&v);
@@ -492,10 +497,10 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
 
 extern "C" int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K,
                                     long lda, long ldw, long ldo, int tile_n, void* stream) {
-  const bool relu2 = (mode & GI_ACT_RELU2) != 0;
-  const int act = relu2 ? 2 : ((mode & GI_ACT_GELU) ? 1 : 0);
+  const bool relu2 = (mode & GI_ACT_RELU2) != 0, gelu_erf = (mode & GI_ACT_GELU_ERF) != 0;
+  const int act = relu2 ? 2 : (gelu_erf ? 3 : ((mode & GI_ACT_GELU) ? 1 : 0));
   mode &= 0xff;
-  if (relu2 ? mode != GI_TC_STORE_BF16 : (act && mode != GI_TC_SWIGLU))
+  if ((relu2 || gelu_erf) ? (mode != GI_TC_STORE_BF16 || (relu2 && gelu_erf)) : (act && mode != GI_TC_SWIGLU))
     return gi::fail(GI_ERR_ARG, "tensor-core product: an activation without the mode that applies it");
   if (bias != nullptr && !relu2) return gi::fail(GI_ERR_ARG, "tensor-core product: a bias goes with the squared relu's store");
   if (M <= 0 || N <= 0) return GI_OK;

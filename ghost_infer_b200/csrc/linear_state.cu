@@ -18,9 +18,11 @@
 // token, since the next write depends on it; the read-outs S^T q of eight tokens are exchanged together (seven exchanges
 // instead of twenty-four).  The order of every sum follows from K alone: one token or a thousand, alone or in a batch,
 // whatever the tile, give the same bits.
-// Four more warps of the block prepare the next tokens while these work: they load a chunk's rows, apply silu, unit norms,
-// the decay and the write strength (one warp per token), and write the previous chunk's read-outs to memory in whole
-// lines.  Two buffers in shared memory, one barrier per chunk.
+// Four more warps of the block prepare the next tokens while these work: together they load a chunk's rows (sixteen bytes a
+// thread where the rows allow it, every load before anything is computed from it, so a chunk costs one trip to memory),
+// apply silu on the way into shared memory, then the unit norms (one warp per token, in place), the decay and the write
+// strength, and write the previous chunk's read-outs to memory in whole lines.  Two buffers in shared memory, one barrier
+// of the block per chunk.
 // State per slot: [heads][V][K] floats (a column's rows side by side) at the start of the slot's row; slot -1 (a padding row
 // of a fixed-size launch) uses the last row of the matrix.
 #include <math.h>
@@ -50,6 +52,23 @@ __device__ __forceinline__ void ls_halve(float (&v)[LS_TB], int lane) {
   }
 }
 
+// Sixteen bytes of a row as 32-bit numbers.
+__device__ __forceinline__ void ls_load16(const float* p, float (&out)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void ls_load16(const __nv_bfloat16* p, float (&out)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+// The preparing threads among themselves (barrier 1; the block's own barrier is 0).
+__device__ __forceinline__ void ls_prep_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(LS_PREP) : "memory"); }
+
 struct LsArgs {
   float* o;
   const void *q, *k, *v, *a_in, *b_in;
@@ -59,7 +78,7 @@ struct LsArgs {
   long state_ld;
   int state_rows;
   const int *cu_seqlens, *seq_slots;
-  int heads, qk_heads, K, V, in_act, unit_norm, vec_state;
+  int heads, qk_heads, K, V, in_act, unit_norm, vec_state, vec_in;
   float norm_eps, q_scale;
 };
 
@@ -67,13 +86,17 @@ struct LsArgs {
 template <int KR> struct LsChunk { static constexpr int value = KR >= 32 ? 8 : 16; };
 
 template <typename T, int KR, int COLS, bool DELTA>
-__global__ void __launch_bounds__(COLS * LS_LANES + LS_PREP)
+// two blocks an SM for the narrower tiles: a grid of about as many blocks as SMs times two then runs as one round
+__global__ void __launch_bounds__(COLS * LS_LANES + LS_PREP, COLS <= 16 ? 2 : 1)
 linear_state_kernel(const LsArgs a) {
   constexpr int Kp = KR * LS_LANES;            // rows with padding
   constexpr int M = KR / 4;                    // groups of four rows per lane; also a preparing lane's share of a row
   constexpr int NC = COLS * LS_LANES;          // threads that hold S
   constexpr int CH = LsChunk<KR>::value;
   constexpr int BUF = 2 * CH * Kp + 2 * CH * COLS + 2 * CH;
+  constexpr int VW = 16 / (int)sizeof(T);      // numbers of a row in sixteen bytes
+  static_assert(CH % LS_TB == 0 && CH <= LS_PREP && (CH * Kp) % LS_PREP == 0 && COLS % VW == 0 && CH * COLS / VW <= LS_PREP,
+                "whole exchanges; a preparing thread per token, and per group of a chunk's values");
   extern __shared__ __align__(16) float sm[];
   gi::pdl_prologue();
   const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * COLS;
@@ -92,50 +115,119 @@ linear_state_kernel(const LsArgs a) {
   const float dc = a.decay_c[h];
   const float rate = ap != nullptr ? expf(dc) : 0.f, bias = (ap != nullptr && a.dt_bias != nullptr) ? a.dt_bias[h] : 0.f;
 
-  // a chunk's tokens made ready in buffer `buf`: one warp per token
+  // a chunk's tokens made ready in buffer `buf` by the 128 preparing threads together.  First every thread loads its share
+  // of the chunk's rows (sixteen bytes at a time where the rows allow it), all loads before anything is computed from them,
+  // so a chunk costs one trip to memory; silu is applied on the way into shared memory.  Then, for unit vectors, one warp
+  // per token sums the squares of its row in shared memory and scales it in place.
   auto prepare = [&](int c, float* buf) {
     float* sq = buf; float* sk = sq + CH * Kp; float* sv = sk + CH * Kp; float* sg = sv + CH * COLS; float* sb = sg + CH;
     const int n = min(CH, qlen - c * CH);
-    const int pw = (tid - NC) >> 5, pl = tid & 31;
-    for (int t = pw; t < n; t += LS_PREP / 32) {
-      const size_t tok = (size_t)tok0 + (size_t)c * CH + t;
-      float qv[M], kv[M];
-      float s1 = 0.f, s2 = 0.f;
+    const int pt = tid - NC;
+    const size_t tokc = (size_t)tok0 + (size_t)c * CH;
+    const bool act = a.in_act != 0;
+    // decay and write strength: one thread per token
+    float av = 0.f, bv = 0.f;
+    if (pt < n) {
+      if (ap != nullptr) av = gi::ldf(ap + (tokc + pt) * a.lda + h);
+      if (bp != nullptr) bv = gi::ldf(bp + (tokc + pt) * a.ldb + h);
+    }
+    if (a.vec_in) {
+      constexpr int QG = (CH * Kp / VW + LS_PREP - 1) / LS_PREP;     // groups of VW numbers a thread moves, per operand
+      const int gpr = K / VW, total = n * gpr;
+      float qr[QG][VW], kr[QG][VW];
 #pragma unroll
-      for (int i = 0; i < M; ++i) {
-        const int r = pl + 32 * i;
-        qv[i] = 0.f; kv[i] = 0.f;
-        if (r < K) {
-          qv[i] = gi::ldf(qp + tok * a.ldq + (size_t)hk * K + r);
-          kv[i] = gi::ldf(kp + tok * a.ldk + (size_t)hk * K + r);
-          if (a.in_act) { qv[i] = ls_silu(qv[i]); kv[i] = ls_silu(kv[i]); }
+      for (int i = 0; i < QG; ++i) {
+        const int g = pt + i * LS_PREP;
+        if (g < total) {
+          const int t = g / gpr, r0 = (g - t * gpr) * VW;
+          ls_load16(qp + (tokc + t) * a.ldq + (size_t)hk * K + r0, qr[i]);
+          ls_load16(kp + (tokc + t) * a.ldk + (size_t)hk * K + r0, kr[i]);
         }
-        s1 = fmaf(qv[i], qv[i], s1);
-        s2 = fmaf(kv[i], kv[i], s2);
       }
-      float fq = 1.f, fk = 1.f;
-      if (a.unit_norm) {
+      float vr[VW];
+      const int vpr = COLS / VW, vt = pt / vpr, vc = (pt - vt * vpr) * VW;     // at most CH * COLS / VW <= 128 groups
+      const bool vlive = vt < n && j0 + vc < V;
+      if (vlive) ls_load16(vp + (tokc + vt) * a.ldv + (size_t)h * V + j0 + vc, vr);
+#pragma unroll
+      for (int i = 0; i < QG; ++i) {
+        const int g = pt + i * LS_PREP;
+        if (g < total) {
+          const int t = g / gpr, r0 = (g - t * gpr) * VW;
+#pragma unroll
+          for (int e = 0; e < VW; e += 4) {
+            float4 q4 = make_float4(qr[i][e], qr[i][e + 1], qr[i][e + 2], qr[i][e + 3]);
+            float4 k4 = make_float4(kr[i][e], kr[i][e + 1], kr[i][e + 2], kr[i][e + 3]);
+            if (act) {
+              q4.x = ls_silu(q4.x); q4.y = ls_silu(q4.y); q4.z = ls_silu(q4.z); q4.w = ls_silu(q4.w);
+              k4.x = ls_silu(k4.x); k4.y = ls_silu(k4.y); k4.z = ls_silu(k4.z); k4.w = ls_silu(k4.w);
+            }
+            *reinterpret_cast<float4*>(sq + t * Kp + r0 + e) = q4;
+            *reinterpret_cast<float4*>(sk + t * Kp + r0 + e) = k4;
+          }
+        }
+      }
+      if (vlive) {
+#pragma unroll
+        for (int e = 0; e < VW; ++e) sv[vt * COLS + vc + e] = act ? ls_silu(vr[e]) : vr[e];     // V is a multiple of VW here
+      }
+    } else {
+      constexpr int QS = CH * Kp / LS_PREP, VS = (CH * COLS + LS_PREP - 1) / LS_PREP;
+      const int total = n * K;
+      float qr[QS], kr[QS], vr[VS];
+#pragma unroll
+      for (int i = 0; i < QS; ++i) {
+        const int e = pt + i * LS_PREP;
+        if (e < total) {
+          const int t = e / K, r = e - t * K;
+          qr[i] = gi::ldf(qp + (tokc + t) * a.ldq + (size_t)hk * K + r);
+          kr[i] = gi::ldf(kp + (tokc + t) * a.ldk + (size_t)hk * K + r);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VS; ++i) {
+        const int e = pt + i * LS_PREP, t = e / COLS, cc = e % COLS;
+        vr[i] = (t < n && j0 + cc < V) ? gi::ldf(vp + (tokc + t) * a.ldv + (size_t)h * V + j0 + cc) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < QS; ++i) {
+        const int e = pt + i * LS_PREP;
+        if (e < total) {
+          const int t = e / K, r = e - t * K;
+          sq[t * Kp + r] = act ? ls_silu(qr[i]) : qr[i];
+          sk[t * Kp + r] = act ? ls_silu(kr[i]) : kr[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VS; ++i) {
+        const int e = pt + i * LS_PREP;
+        if (e < n * COLS) sv[e] = act ? ls_silu(vr[i]) : vr[i];
+      }
+    }
+    if (pt < n) {
+      sg[pt] = ap != nullptr ? expf(-rate * ls_softplus(av + bias)) : dc;
+      sb[pt] = bp != nullptr ? 1.0f / (1.0f + expf(-bv)) : 1.0f;
+    }
+    if (a.unit_norm) {
+      ls_prep_barrier();             // the chunk's rows are in shared memory
+      const int pw = pt >> 5, pl = pt & 31;
+      for (int t = pw; t < n; t += LS_PREP / 32) {
+        float qv[M], kv[M];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < M; ++i) {
+          qv[i] = sq[t * Kp + pl + 32 * i];
+          kv[i] = sk[t * Kp + pl + 32 * i];
+          s1 = fmaf(qv[i], qv[i], s1);
+          s2 = fmaf(kv[i], kv[i], s2);
+        }
         s1 = gi::warp_sum(s1);
         s2 = gi::warp_sum(s2);
-        fq = a.q_scale / sqrtf(s1 + a.norm_eps);
-        fk = 1.0f / sqrtf(s2 + a.norm_eps);
-      }
+        const float fq = a.q_scale / sqrtf(s1 + a.norm_eps), fk = 1.0f / sqrtf(s2 + a.norm_eps);
 #pragma unroll
-      for (int i = 0; i < M; ++i) {
-        sq[t * Kp + pl + 32 * i] = qv[i] * fq;
-        sk[t * Kp + pl + 32 * i] = kv[i] * fk;
-      }
-      for (int cc = pl; cc < COLS; cc += 32) {
-        float vv = 0.f;
-        if (j0 + cc < V) {
-          vv = gi::ldf(vp + tok * a.ldv + (size_t)h * V + j0 + cc);
-          if (a.in_act) vv = ls_silu(vv);
+        for (int i = 0; i < M; ++i) {
+          sq[t * Kp + pl + 32 * i] = qv[i] * fq;
+          sk[t * Kp + pl + 32 * i] = kv[i] * fk;
         }
-        sv[t * COLS + cc] = vv;
-      }
-      if (pl == 0) {
-        sg[t] = ap != nullptr ? expf(-rate * ls_softplus(gi::ldf(ap + tok * a.lda + h) + bias)) : dc;
-        sb[t] = bp != nullptr ? 1.0f / (1.0f + expf(-gi::ldf(bp + tok * a.ldb + h))) : 1.0f;
       }
     }
   };
@@ -153,6 +245,12 @@ linear_state_kernel(const LsArgs a) {
   const int j = j0 + col;
   float S[KR];
   if (prep) {
+    if (K < Kp) {                  // rows past K stay zero in both buffers: nothing writes them again
+      for (int e = tid - NC; e < 2 * CH * Kp; e += LS_PREP) {
+        if (e % Kp >= K) { sm[e] = 0.f; sm[BUF + e] = 0.f; }
+      }
+      ls_prep_barrier();
+    }
     prepare(0, sm);
   } else {
 #pragma unroll
@@ -179,51 +277,57 @@ linear_state_kernel(const LsArgs a) {
     const float* sg = sv + CH * COLS; const float* sb = sg + CH;
     float* so = buf + 2 * CH * Kp + CH * COLS + 2 * CH;
     const int n = min(CH, qlen - c * CH);
+    // one token: the state's columns walk on, `out` takes this lane's share of the read-out
+    auto token = [&](int t, float& out) {
+      const float g = sg[t];
+      float kk[KR], qq[KR];
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float4 k4 = *reinterpret_cast<const float4*>(sk + t * Kp + 4 * (lane + LS_LANES * m));
+        const float4 q4 = *reinterpret_cast<const float4*>(sq + t * Kp + 4 * (lane + LS_LANES * m));
+        kk[4 * m] = k4.x; kk[4 * m + 1] = k4.y; kk[4 * m + 2] = k4.z; kk[4 * m + 3] = k4.w;
+        qq[4 * m] = q4.x; qq[4 * m + 1] = q4.y; qq[4 * m + 2] = q4.z; qq[4 * m + 3] = q4.w;
+      }
+      float u = sv[t * COLS + col];
+      if (DELTA) {
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;     // four chains, then a tree: the order is fixed by K alone
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          d0 = fmaf(S[4 * m], kk[4 * m], d0);
+          d1 = fmaf(S[4 * m + 1], kk[4 * m + 1], d1);
+          d2 = fmaf(S[4 * m + 2], kk[4 * m + 2], d2);
+          d3 = fmaf(S[4 * m + 3], kk[4 * m + 3], d3);
+        }
+        float d = (d0 + d1) + (d2 + d3);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        u = sb[t] * (u - g * d);
+      }
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        S[4 * m] = fmaf(kk[4 * m], u, g * S[4 * m]);
+        S[4 * m + 1] = fmaf(kk[4 * m + 1], u, g * S[4 * m + 1]);
+        S[4 * m + 2] = fmaf(kk[4 * m + 2], u, g * S[4 * m + 2]);
+        S[4 * m + 3] = fmaf(kk[4 * m + 3], u, g * S[4 * m + 3]);
+        a0 = fmaf(S[4 * m], qq[4 * m], a0);
+        a1 = fmaf(S[4 * m + 1], qq[4 * m + 1], a1);
+        a2 = fmaf(S[4 * m + 2], qq[4 * m + 2], a2);
+        a3 = fmaf(S[4 * m + 3], qq[4 * m + 3], a3);
+      }
+      out = (a0 + a1) + (a2 + a3);
+    };
     for (int t0 = 0; t0 < n; t0 += LS_TB) {
       float acc[LS_TB];
+      if (t0 + LS_TB <= n) {     // eight whole tokens: nothing to test between them, so the next one's loads start early
 #pragma unroll
-      for (int tl = 0; tl < LS_TB; ++tl) {
-        const int t = t0 + tl;
-        acc[tl] = 0.f;
-        if (t < n) {             // the same for the whole block
-          const float g = sg[t];
-          float kk[KR], qq[KR];
+        for (int tl = 0; tl < LS_TB; ++tl) token(t0 + tl, acc[tl]);
+      } else {
 #pragma unroll
-          for (int m = 0; m < M; ++m) {
-            const float4 k4 = *reinterpret_cast<const float4*>(sk + t * Kp + 4 * (lane + LS_LANES * m));
-            const float4 q4 = *reinterpret_cast<const float4*>(sq + t * Kp + 4 * (lane + LS_LANES * m));
-            kk[4 * m] = k4.x; kk[4 * m + 1] = k4.y; kk[4 * m + 2] = k4.z; kk[4 * m + 3] = k4.w;
-            qq[4 * m] = q4.x; qq[4 * m + 1] = q4.y; qq[4 * m + 2] = q4.z; qq[4 * m + 3] = q4.w;
-          }
-          float u = sv[t * COLS + col];
-          if (DELTA) {
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;     // four chains, then a tree: the order is fixed by K alone
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-              d0 = fmaf(S[4 * m], kk[4 * m], d0);
-              d1 = fmaf(S[4 * m + 1], kk[4 * m + 1], d1);
-              d2 = fmaf(S[4 * m + 2], kk[4 * m + 2], d2);
-              d3 = fmaf(S[4 * m + 3], kk[4 * m + 3], d3);
-            }
-            float d = (d0 + d1) + (d2 + d3);
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            u = sb[t] * (u - g * d);
-          }
-          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            S[4 * m] = fmaf(kk[4 * m], u, g * S[4 * m]);
-            S[4 * m + 1] = fmaf(kk[4 * m + 1], u, g * S[4 * m + 1]);
-            S[4 * m + 2] = fmaf(kk[4 * m + 2], u, g * S[4 * m + 2]);
-            S[4 * m + 3] = fmaf(kk[4 * m + 3], u, g * S[4 * m + 3]);
-            a0 = fmaf(S[4 * m], qq[4 * m], a0);
-            a1 = fmaf(S[4 * m + 1], qq[4 * m + 1], a1);
-            a2 = fmaf(S[4 * m + 2], qq[4 * m + 2], a2);
-            a3 = fmaf(S[4 * m + 3], qq[4 * m + 3], a3);
-          }
-          acc[tl] = (a0 + a1) + (a2 + a3);
+        for (int tl = 0; tl < LS_TB; ++tl) {
+          acc[tl] = 0.f;
+          if (t0 + tl < n) token(t0 + tl, acc[tl]);      // the same for the whole block
         }
       }
       ls_halve<4, 4>(acc, lane);
@@ -300,6 +404,13 @@ extern "C" int gi_linear_state(float* o, const void* q, long ldq, const void* k,
   // sixteen bytes of a column at a time where every column of every slot starts on such a boundary
   a.vec_state = (K % 4 == 0 && state_ld % 4 == 0 && ((size_t)state & 15) == 0) ? 1 : 0;
   a.norm_eps = norm_eps; a.q_scale = q_scale;
+  {
+    // sixteen bytes of a row at a time where every piece a block reads starts on such a boundary
+    const int vw = dtype == GI_BF16 ? 8 : 4;
+    const size_t esz = dtype == GI_BF16 ? 2 : 4;
+    a.vec_in = (K % vw == 0 && V % vw == 0 && ldq % vw == 0 && ldk % vw == 0 && ldv % vw == 0 &&
+                (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && esz * vw == 16) ? 1 : 0;
+  }
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T, {
     if (K <= 4 * LS_LANES) e = ls_pick_tile<T, 4>(a, n_seqs, delta != 0, (cudaStream_t)stream);

@@ -34,35 +34,75 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 __device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
 
-template <typename TO>
-__global__ void cast_rows_kernel(TO* __restrict__ out, const float* x, size_t total) {
-  gi::pdl_prologue();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < total) gi::stf(out + i, x[i]);
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
 }
 
-// One block per row; the order of the row's sum follows from the width alone.
+// Four values a thread; `vec`: both pointers are 16-byte aligned, so whole groups move as one access each way.
+template <typename TO>
+__global__ void cast_rows_kernel(TO* __restrict__ out, const float* x, size_t total, int vec) {
+  gi::pdl_prologue();
+  const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (e >= total) return;
+  if (vec && e + 4 <= total) {
+    st4(out + e, *reinterpret_cast<const float4*>(x + e));
+  } else {
+    for (size_t i = e; i < total && i < e + 4; ++i) gi::stf(out + i, x[i]);
+  }
+}
+
+// One block per row.  A thread takes groups of four neighbouring values, 1,024 values apart; `vec`: the rows start on
+// 16-byte boundaries, so a group is one access.  The order of the row's sum follows from the width alone either way.
 template <typename TW>
 __global__ void __launch_bounds__(256)
-postnorm_add_kernel(float* x, const float* y, const TW* __restrict__ w, const TW* __restrict__ s, int d, float eps) {
+postnorm_add_kernel(float* x, const float* y, const TW* __restrict__ w, const TW* __restrict__ s, int d, float eps, int vec) {
   __shared__ float scratch[33];
   gi::pdl_prologue();
   const float* yr = y + (size_t)blockIdx.x * d;
   float* xr = x + (size_t)blockIdx.x * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += 256) ss = fmaf(yr[i], yr[i], ss);
+  for (int i = threadIdx.x * 4; i < d; i += 1024) {
+    if (vec && i + 4 <= d) {
+      const float4 v = *reinterpret_cast<const float4*>(yr + i);
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    } else {
+      for (int e = i; e < d && e < i + 4; ++e) ss = fmaf(yr[e], yr[e], ss);
+    }
+  }
   const float rs = 1.0f / sqrtf(gi::block_sum(ss, scratch) / (float)d + eps);
-  for (int i = threadIdx.x; i < d; i += 256) {
-    float v = yr[i] * rs * gi::ldf(w + i);
-    if (s != nullptr) v *= gi::ldf(s + i);
-    xr[i] += v;
+  for (int i = threadIdx.x * 4; i < d; i += 1024) {
+    if (vec && i + 4 <= d) {
+      const float4 v = *reinterpret_cast<const float4*>(yr + i);
+      float4 o = *reinterpret_cast<const float4*>(xr + i);
+      float t0 = v.x * rs * gi::ldf(w + i), t1 = v.y * rs * gi::ldf(w + i + 1), t2 = v.z * rs * gi::ldf(w + i + 2),
+            t3 = v.w * rs * gi::ldf(w + i + 3);
+      if (s != nullptr) { t0 *= gi::ldf(s + i); t1 *= gi::ldf(s + i + 1); t2 *= gi::ldf(s + i + 2); t3 *= gi::ldf(s + i + 3); }
+      o.x += t0; o.y += t1; o.z += t2; o.w += t3;
+      *reinterpret_cast<float4*>(xr + i) = o;
+    } else {
+      for (int e = i; e < d && e < i + 4; ++e) {
+        float v = yr[e] * rs * gi::ldf(w + e);
+        if (s != nullptr) v *= gi::ldf(s + e);
+        xr[e] += v;
+      }
+    }
   }
 }
 
-__global__ void axpy_kernel(float* out, const float* a, float alpha, size_t total) {
+__global__ void axpy_kernel(float* out, const float* a, float alpha, size_t total, int vec) {
   gi::pdl_prologue();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < total) out[i] = fmaf(alpha, a[i], out[i]);
+  const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (e >= total) return;
+  if (vec && e + 4 <= total) {
+    const float4 v = *reinterpret_cast<const float4*>(a + e);
+    float4 o = *reinterpret_cast<const float4*>(out + e);
+    o.x = fmaf(alpha, v.x, o.x); o.y = fmaf(alpha, v.y, o.y); o.z = fmaf(alpha, v.z, o.z); o.w = fmaf(alpha, v.w, o.w);
+    *reinterpret_cast<float4*>(out + e) = o;
+  } else {
+    for (size_t i = e; i < total && i < e + 4; ++i) out[i] = fmaf(alpha, a[i], out[i]);
+  }
 }
 
 // One block per token.  Shared memory: the row's queries and keys as 32-bit numbers.
@@ -193,8 +233,8 @@ extern "C" int gi_cast_rows(void* out, int out_dtype, const float* x, long n_val
   if (n_values <= 0) return GI_OK;
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(out_dtype, TO,
-      e = gi::launch(cast_rows_kernel<TO>, dim3(blocks_of((size_t)n_values)), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x,
-                     (size_t)n_values));
+      e = gi::launch(cast_rows_kernel<TO>, dim3(blocks_of(((size_t)n_values + 3) / 4)), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x,
+                     (size_t)n_values, (int)((((uintptr_t)out | (uintptr_t)x) & 15) == 0)));
   return gi::check(e, "cast_rows");
 }
 
@@ -205,14 +245,14 @@ extern "C" int gi_postnorm_add(float* x, const float* y, const void* w, const vo
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(postnorm_add_kernel<TW>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, x, y, (const TW*)w,
-                     (const TW*)scale, d, eps));
+                     (const TW*)scale, d, eps, (int)(d % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)));
   return gi::check(e, "postnorm_add");
 }
 
 extern "C" int gi_axpy(float* out, const float* a, float alpha, long n_values, void* stream) {
   if (n_values <= 0) return GI_OK;
-  cudaError_t e = gi::launch(axpy_kernel, dim3(blocks_of((size_t)n_values)), dim3(256), 0, (cudaStream_t)stream, out, a, alpha,
-                             (size_t)n_values);
+  cudaError_t e = gi::launch(axpy_kernel, dim3(blocks_of(((size_t)n_values + 3) / 4)), dim3(256), 0, (cudaStream_t)stream, out, a, alpha,
+                             (size_t)n_values, (int)((((uintptr_t)out | (uintptr_t)a) & 15) == 0));
   return gi::check(e, "axpy");
 }
 

@@ -6,7 +6,8 @@
 Kernels: gemm_stream, gemm_skinny (decode products), gemm_tc (prefill product), attn_decode, attn_prefill (mma.sync),
 attn_prefill_t5 (tcgen05), attn_latent_decode, attn_latent_prefill (attention over one shared latent row per position:
 --heads, --rank, --rot-dim),
-rmsnorm, rope, sample.  Operands rotate through enough different buffers to exceed the L2 cache, so a bytes
+linear_state, mamba2_scan (the token-by-token recurrences: --batch, --context, --heads, --kv-heads, --head-dim, --v-dim,
+--delta), rmsnorm, rope, sample.  Operands rotate through enough different buffers to exceed the L2 cache, so a bytes
 figure is a DRAM figure.  The same command under `ncu --clock-control none -k regex:<kernel> -c 3` profiles exactly these launches.
 The reference times whole runs only (`bench`, src/main.rs:1241-1285) and, per operation, wall-clock buckets
 (src/profile.rs:7-46); per-kernel device timing is what a roofline needs.
@@ -61,6 +62,8 @@ def main() -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--rank", type=int, default=512, help="attn_latent_*: numbers of the latent (the values' width)")
     ap.add_argument("--rot-dim", type=int, default=64, help="attn_latent_*: numbers of the rotated key part behind the latent")
+    ap.add_argument("--v-dim", type=int, default=0, help="linear_state, mamba2_scan: columns of a head's state (default: --head-dim)")
+    ap.add_argument("--delta", type=int, default=0, help="linear_state: 1 = the gated delta rule (--kv-heads query/key heads), 0 = a constant decay")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--own-tiles", type=int, default=0, help="attn_decode: slices of that many tiles of each sequence's own span")
     ap.add_argument("--tile-keys", type=int, default=0, help="attn_decode: 16 or 32 keys per tile (default: the engine's)")
@@ -180,6 +183,45 @@ def main() -> int:
             flops = 2.0 * B * H * (dk + r) * S * (S + 1) / 2
             out.update(shape=[B, S, H, r, dr], us=round(us, 2), tflops=round(flops / us / 1e6, 1),
                        frac_tensor=round(flops / us / 1e6 / tflops, 3))
+    elif args.kernel in ("linear_state", "mamba2_scan"):
+        # the token-by-token recurrences: --batch sequences of --context tokens each (--context 1: a decode step), --heads
+        # heads of a --head-dim x --v-dim state (mamba2_scan: --v-dim columns per head, --head-dim rows of state)
+        from types import SimpleNamespace
+        B, S, H, K = args.batch, args.context, args.heads, args.head_dim
+        V = args.v_dim or K
+        n = B * S
+        step = SimpleNamespace(n_seqs=B, cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=dev) * S,
+                               seq_slots=torch.arange(B, dtype=torch.int32, device=dev))
+        passes = 2      # a state entry is decayed and written, then read out
+        if args.kernel == "linear_state":
+            G = args.kv_heads if args.delta else H
+            rows = torch.randn(n, 2 * G * K + H * V + 2 * H, device=dev, dtype=bf)
+            q, k, v = rows[:, :G * K], rows[:, G * K:2 * G * K], rows[:, 2 * G * K:2 * G * K + H * V]
+            state = torch.zeros(B + 1, H * K * V, device=dev)
+            if args.delta:
+                passes = 3
+                a_log, dt_bias = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+                fn = lambda i: ops.linear_state(q, k, v, state, step, H, G, K, V, a_log, decay_in=rows[:, -H:], dt_bias=dt_bias,
+                                                beta_in=rows[:, -2 * H:-H], unit_norm=True, q_scale=K ** -0.5, delta=True)
+            else:
+                decay = torch.full((H,), 0.99, device=dev)
+                fn = lambda i: ops.linear_state(q, k, v, state, step, H, H, K, V, decay, in_act=True)
+        else:
+            G, taps = args.kv_heads, 4
+            inner, channels = H * V, H * V + 2 * G * K
+            xbc = torch.randn(n, channels, device=dev, dtype=bf)
+            proj = torch.randn(n, 2 * inner + 2 * G * K + H, device=dev, dtype=bf)
+            consts = [torch.zeros(H, device=dev) for _ in range(3)]
+            state = torch.zeros(B + 1, H * K * V + (taps - 1) * channels, device=dev)
+            fn = lambda i: ops.mamba2_scan(xbc, proj, consts[0], consts[1], consts[2], state, step, H, V, K, G, taps)
+        us = _time(fn, 1, args.iters, args.warmup)
+        # 32-bit multiply-adds: one per state entry and pass; the peak is 128 lanes per SM at the clock's maximum
+        props = torch.cuda.get_device_properties(0)
+        fma, peak = float(passes) * n * H * K * V, props.multi_processor_count * 128 * props.clock_rate * 1e3
+        nbytes = 2.0 * B * H * K * V * 4 + n * H * V * 4
+        out.update(shape=[B, S, H, G, K, V], delta=int(args.delta), us=round(us, 2), ns_per_token=round(us * 1e3 / S, 1),
+                   gfma_per_s=round(fma / us / 1e3, 1), frac_fp32=round(fma / us * 1e6 / peak, 3),
+                   gbs=round(nbytes / us / 1e3, 1), frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
     elif args.kernel == "rmsnorm":
         x = torch.randn(args.m, args.k, device=dev)
         w = torch.ones(args.k, device=dev, dtype=bf)

@@ -1703,13 +1703,16 @@ def bias_act(rows: torch.Tensor, bias: Optional[torch.Tensor], act: Optional[str
 
 
 ACT_RELU2 = 0x200       # or-ed into SKINNY_STORE_BF16 for the tensor-core product: relu(sum + bias)^2
+ACT_GELU_ERF = 0x400    # the same: gelu(sum) in its exact (erf) form, no bias
 
 
 def linear_act(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act: str = "relu2") -> torch.Tensor:
-    """act(h W^T + bias) in h's type (`act` "relu2": relu squared).  A prompt step's product on the tensor cores adds the
-    bias and applies the activation in its epilogue; other products are followed by `bias_act`."""
-    if act != "relu2":
-        raise KernelError(f"unknown activation \"{act}\" (relu2)")
+    """act(h W^T + bias) in h's type (`act` "relu2": relu squared; "gelu": the exact (erf) form, without a bias).  A prompt
+    step's product on the tensor cores adds the bias and applies the activation in its epilogue, on the 32-bit sums; other
+    products are followed by `bias_act` or `gelu_rows`."""
+    if act not in ("relu2", "gelu") or (act == "gelu" and bias is not None):
+        raise KernelError(f"unknown activation \"{act}\" (relu2, or gelu without a bias)")
+    flag = ACT_RELU2 if act == "relu2" else ACT_GELU_ERF
     if (tc_ok(h, w) and h.shape[0] > SKINNY_MAX_ROWS and w.shape[0] % 8 == 0
             and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == w.shape[0]))):
         lib = _bind()
@@ -1717,10 +1720,12 @@ def linear_act(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], a
         m, k = h.shape
         n = w.shape[0]
         out = torch.empty((m, n), dtype=torch.bfloat16, device=h.device)
-        _check(lib, lib.gi_gemm_tc_bf16_bias(out.data_ptr(), SKINNY_STORE_BF16 | ACT_RELU2, h.data_ptr(), w.data_ptr(),
+        _check(lib, lib.gi_gemm_tc_bf16_bias(out.data_ptr(), SKINNY_STORE_BF16 | flag, h.data_ptr(), w.data_ptr(),
                                              bias.data_ptr() if bias is not None else None, m, n, k, _rows(h, "activations"),
                                              _rows(w, "weights"), n, int(TC_TILE_N), _stream()))
         return out
+    if act == "gelu":
+        return gelu_rows(linear(h, w, out_dtype=h.dtype))
     return bias_act(linear(h, w, out_dtype=h.dtype), bias, act)
 
 

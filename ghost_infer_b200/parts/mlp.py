@@ -104,9 +104,9 @@ class Mlp(FeedForward):
             self.b_up, self.b_down = bu, bd
 
     def forward(self, h, residual, step) -> None:
-        if self.activation == "gelu":           # the exact (erf) form, as a step of its own between the two products
+        if self.activation == "gelu":           # the exact (erf) form: in a prompt step's product, else a step of its own
             with ops.bucket("ffn matmul"):
-                act = ops.gelu_rows(linear(h, self.w_up, out_dtype=self.rt.dtype))
+                act = ops.linear_act(h, self.w_up, None, "gelu")
                 linear(act, self.w_down, out=residual, accumulate=True)
             return
         with ops.bucket("ffn matmul"):

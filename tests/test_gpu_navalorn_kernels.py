@@ -317,6 +317,22 @@ def test_squared_relu_in_the_product_epilogue(rows, n, k, with_bias):
     torch.testing.assert_close(res.double(), before.double() + rb.double(), rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("rows,n,k", [(70, 136, 96), (300, 264, 128), (65, 8, 8), (129, 520, 72)])
+def test_exact_gelu_in_the_product_epilogue(rows, n, k):
+    g = torch.Generator(device=DEV).manual_seed(rows + 1)
+    h = torch.randn((rows, k), device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn((n, k), device=DEV, generator=g) * 0.3).to(torch.bfloat16)
+    z = h.double() @ w.double().T
+    ref = 0.5 * z * (1.0 + torch.erf(z / math.sqrt(2.0)))
+    got = ops.linear_act(h, w, None, "gelu")                       # many rows: the activation on the product's 32-bit sums
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (rows, n)
+    torch.testing.assert_close(got.double(), ref, rtol=1e-2, atol=1e-2)
+    few = ops.linear_act(h[:9], w, None, "gelu")                   # few rows: product, then the activation
+    torch.testing.assert_close(few.double(), ref[:9], rtol=2e-2, atol=2e-2)
+    with pytest.raises(ops.KernelError):
+        ops.linear_act(h, w, torch.zeros((n,), device=DEV, dtype=torch.bfloat16), "gelu")
+
+
 def test_ungated_experts_stretch_by_stretch():
     experts, width, ff = 5, 64, 40
     g = torch.Generator(device=DEV).manual_seed(1)
