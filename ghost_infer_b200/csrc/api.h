@@ -427,6 +427,11 @@ int gi_cast_rows(void* out, int out_dtype, const float* x, long n_values, void* 
 // x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w [* scale], float32 rows of d numbers; scale may be null.
 int gi_postnorm_add(float* x, const float* y, const void* w, const void* scale, int w_dtype, int n_rows, int d, float eps,
                     void* stream);
+// gi_cast_rows that also sets `zero` (float32, n_values, or null) to zero; gi_postnorm_add that also writes the new rows
+// of x in the type `h_dtype` to `h_out` (or null) and, with `zero_y`, sets y to zero once it is read.
+int gi_cast_rows_zero(void* out, int out_dtype, const float* x, float* zero, long n_values, void* stream);
+int gi_postnorm_add_ex(float* x, float* y, const void* w, const void* scale, int w_dtype, int n_rows, int d, float eps,
+                       void* h_out, int h_dtype, int zero_y, void* stream);
 // out += alpha * a over n_values float32 numbers.
 int gi_axpy(float* out, const float* a, float alpha, long n_values, void* stream);
 // One token's float32 row [q: n_heads * hd | k: n_kv * hd | v: n_kv * hdv] (n_kv 0: queries only): biases (each may be

@@ -41,27 +41,36 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 }
 
 // Four values a thread; `vec`: both pointers are 16-byte aligned, so whole groups move as one access each way.
+// `zero` (or null): float32 values of the same count that are set to zero in the same pass (the rows a sublayer adds into).
 template <typename TO>
-__global__ void cast_rows_kernel(TO* __restrict__ out, const float* x, size_t total, int vec) {
+__global__ void cast_rows_kernel(TO* __restrict__ out, const float* x, float* __restrict__ zero, size_t total, int vec) {
   gi::pdl_prologue();
   const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (e >= total) return;
   if (vec && e + 4 <= total) {
     st4(out + e, *reinterpret_cast<const float4*>(x + e));
+    if (zero != nullptr) *reinterpret_cast<float4*>(zero + e) = make_float4(0.f, 0.f, 0.f, 0.f);
   } else {
-    for (size_t i = e; i < total && i < e + 4; ++i) gi::stf(out + i, x[i]);
+    for (size_t i = e; i < total && i < e + 4; ++i) {
+      gi::stf(out + i, x[i]);
+      if (zero != nullptr) zero[i] = 0.f;
+    }
   }
 }
 
 // One block per row.  A thread takes groups of four neighbouring values, 1,024 values apart; `vec`: the rows start on
 // 16-byte boundaries, so a group is one access.  The order of the row's sum follows from the width alone either way.
-template <typename TW>
+// `h_out` (or null): the new rows of x once more in the activation type, what the next sublayer reads; `zero_y`: y is set
+// to zero once it is read, for the next sublayer to add into.
+template <typename TW, typename TH>
 __global__ void __launch_bounds__(256)
-postnorm_add_kernel(float* x, const float* y, const TW* __restrict__ w, const TW* __restrict__ s, int d, float eps, int vec) {
+postnorm_add_kernel(float* x, float* y, const TW* __restrict__ w, const TW* __restrict__ s, int d, float eps, int vec,
+                    TH* __restrict__ h_out, int zero_y) {
   __shared__ float scratch[33];
   gi::pdl_prologue();
-  const float* yr = y + (size_t)blockIdx.x * d;
+  float* yr = y + (size_t)blockIdx.x * d;
   float* xr = x + (size_t)blockIdx.x * d;
+  TH* hr = h_out != nullptr ? h_out + (size_t)blockIdx.x * d : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x * 4; i < d; i += 1024) {
     if (vec && i + 4 <= d) {
@@ -81,11 +90,16 @@ postnorm_add_kernel(float* x, const float* y, const TW* __restrict__ w, const TW
       if (s != nullptr) { t0 *= gi::ldf(s + i); t1 *= gi::ldf(s + i + 1); t2 *= gi::ldf(s + i + 2); t3 *= gi::ldf(s + i + 3); }
       o.x += t0; o.y += t1; o.z += t2; o.w += t3;
       *reinterpret_cast<float4*>(xr + i) = o;
+      if (hr != nullptr) st4(hr + i, o);
+      if (zero_y) *reinterpret_cast<float4*>(yr + i) = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
       for (int e = i; e < d && e < i + 4; ++e) {
         float v = yr[e] * rs * gi::ldf(w + e);
         if (s != nullptr) v *= gi::ldf(s + e);
-        xr[e] += v;
+        const float o = xr[e] + v;
+        xr[e] = o;
+        if (hr != nullptr) gi::stf(hr + e, o);
+        if (zero_y) yr[e] = 0.f;
       }
     }
   }
@@ -230,22 +244,32 @@ inline unsigned blocks_of(size_t total) { return (unsigned)((total + 255) / 256)
 }  // namespace
 
 extern "C" int gi_cast_rows(void* out, int out_dtype, const float* x, long n_values, void* stream) {
+  return gi_cast_rows_zero(out, out_dtype, x, nullptr, n_values, stream);
+}
+
+extern "C" int gi_cast_rows_zero(void* out, int out_dtype, const float* x, float* zero, long n_values, void* stream) {
   if (n_values <= 0) return GI_OK;
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(out_dtype, TO,
       e = gi::launch(cast_rows_kernel<TO>, dim3(blocks_of(((size_t)n_values + 3) / 4)), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x,
-                     (size_t)n_values, (int)((((uintptr_t)out | (uintptr_t)x) & 15) == 0)));
+                     zero, (size_t)n_values, (int)((((uintptr_t)out | (uintptr_t)x | (uintptr_t)zero) & 15) == 0)));
   return gi::check(e, "cast_rows");
 }
 
 extern "C" int gi_postnorm_add(float* x, const float* y, const void* w, const void* scale, int w_dtype, int n_rows, int d,
                                float eps, void* stream) {
+  return gi_postnorm_add_ex(x, const_cast<float*>(y), w, scale, w_dtype, n_rows, d, eps, nullptr, GI_F32, 0, stream);
+}
+
+extern "C" int gi_postnorm_add_ex(float* x, float* y, const void* w, const void* scale, int w_dtype, int n_rows, int d, float eps,
+                                  void* h_out, int h_dtype, int zero_y, void* stream) {
   if (n_rows <= 0) return GI_OK;
   if (d <= 0 || !x || !y || !w) return gi::fail(GI_ERR_ARG, "postnorm_add: bad width %d or a missing pointer", d);
+  const int vec = (int)(d % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)h_out) & 15) == 0);
   cudaError_t e = cudaSuccess;
-  GI_DISPATCH_DTYPE(w_dtype, TW,
-      e = gi::launch(postnorm_add_kernel<TW>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, x, y, (const TW*)w,
-                     (const TW*)scale, d, eps, (int)(d % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)));
+  GI_DISPATCH_DTYPE(w_dtype, TW, GI_DISPATCH_DTYPE(h_dtype, TH,
+      e = gi::launch(postnorm_add_kernel<TW, TH>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, x, y, (const TW*)w,
+                     (const TW*)scale, d, eps, vec, (TH*)h_out, zero_y)));
   return gi::check(e, "postnorm_add");
 }
 

@@ -104,6 +104,8 @@ def _bind():
         "gi_moe_experts_tc_ungated": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
         "gi_cast_rows": [P, I, P, L, P],
         "gi_postnorm_add": [P, P, P, P, I, I, I, F, P],
+        "gi_cast_rows_zero": [P, I, P, P, L, P],
+        "gi_postnorm_add_ex": [P, P, P, P, I, I, I, F, P, I, I, P],
         "gi_axpy": [P, P, F, L, P],
         "gi_qk_prepare": [P, L, I, P, L, P, P, P, P, P, I, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, I, P],
         "gi_gate_mul": [P, P, P, L, I, I, I, I, P],
@@ -1877,21 +1879,29 @@ def attention_latent(qa: torch.Tensor, memory, step, n_heads: int, rank: int, ro
 
 # ------------------------------------------------------------------------------------------------
 # Layers that read the stream itself and norm a sublayer's output; attention with normed, rotated queries and keys.
-def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    """The float32 stream in the activation type; in the 32-bit path the stream itself."""
+def cast_rows(x: torch.Tensor, dtype: torch.dtype, zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The float32 stream in the activation type; in the 32-bit path the stream itself.  `zero`: float32 rows of the
+    stream's shape that are set to zero on the way (what a sublayer will add into)."""
     _cuda(x, "residual stream")
     if x.dtype != torch.float32 or not x.is_contiguous():
         raise KernelError("the stream's rows must be contiguous float32")
+    if zero is not None and (zero.dtype != torch.float32 or not zero.is_contiguous() or zero.shape != x.shape or not zero.is_cuda):
+        raise KernelError("the rows to set to zero must be contiguous float32 of the stream's shape")
     if dtype == torch.float32:
+        if zero is not None:
+            zero.zero_()
         return x.as_subclass(torch.Tensor) if type(x) is not torch.Tensor else x
     lib = _bind()
     out = torch.empty(x.shape, dtype=dtype, device=x.device)
-    _check(lib, lib.gi_cast_rows(out.data_ptr(), _dt(out, "rows"), x.data_ptr(), x.numel(), _stream()))
+    _check(lib, lib.gi_cast_rows_zero(out.data_ptr(), _dt(out, "rows"), x.data_ptr(), zero.data_ptr() if zero is not None else None,
+                                      x.numel(), _stream()))
     return out
 
 
-def postnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, scale: Optional[torch.Tensor] = None) -> None:
-    """x += y / sqrt(mean(y^2) + eps) * weight [* scale] over float32 rows."""
+def postnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, scale: Optional[torch.Tensor] = None,
+                 cast_out: Optional[torch.Tensor] = None, zero_y: bool = False) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * weight [* scale] over float32 rows.  `cast_out`: rows of x's shape that receive the
+    new x in their own type (what the next sublayer reads); `zero_y`: y is zero afterwards (what it adds into)."""
     lib = _bind()
     _cuda(x, "residual stream")
     _cuda(y, "sublayer output")
@@ -1902,8 +1912,13 @@ def postnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: fl
     for t, what in ((weight, "the norm's weight"), (scale, "the channel scale")):
         if t is not None and (t.numel() != d or not t.is_contiguous() or t.dtype != weight.dtype):
             raise KernelError(f"{what} must hold {d} values of the norm weight's type")
-    _check(lib, lib.gi_postnorm_add(x.data_ptr(), y.data_ptr(), weight.data_ptr(), scale.data_ptr() if scale is not None else None,
-                                    _dt(weight, "norm weight"), n, d, float(eps), _stream()))
+    if cast_out is not None and (not cast_out.is_cuda or not cast_out.is_contiguous() or tuple(cast_out.shape) != (n, d)
+                                 or cast_out.data_ptr() == x.data_ptr()):
+        raise KernelError("the rows that take the new stream must be contiguous, of the stream's shape and not the stream itself")
+    _check(lib, lib.gi_postnorm_add_ex(x.data_ptr(), y.data_ptr(), weight.data_ptr(), scale.data_ptr() if scale is not None else None,
+                                       _dt(weight, "norm weight"), n, d, float(eps),
+                                       cast_out.data_ptr() if cast_out is not None else None,
+                                       _dt(cast_out, "next input") if cast_out is not None else F32, int(bool(zero_y)), _stream()))
 
 
 def axpy(out: torch.Tensor, a: torch.Tensor, alpha: float) -> None:

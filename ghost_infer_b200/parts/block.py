@@ -37,18 +37,24 @@ class ResidualPostNorm(Block):
     `extra["ffn_scale"]`, each optional).  Then every `extra` part named "after..." runs in order as a feed-forward
     on the stream (it adds to it by itself).  Norms, scales and sums are 32-bit."""
 
-    def _sublayer(self, x, norm, scale, run) -> None:
-        h = ops.cast_rows(x, norm.rt.dtype)
-        y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
-        run(h, y)
-        norm.add_normed(x, y, scale.weight if scale is not None else None)
-
     def forward(self, x, step, memory) -> None:
         if x.is_cuda:
             ops.settle(x)             # nothing here defers into the stream; what a layer before left is added first
-        self._sublayer(x, self.mixer_norm, self.extra.get("mixer_scale"), lambda h, y: self.mixer.forward(h, y, step, memory))
+        dt = self.mixer_norm.rt.dtype
+        low = dt != torch.float32     # the 32-bit path reads the stream itself
+        subs = [(self.mixer_norm, self.extra.get("mixer_scale"), lambda h, y: self.mixer.forward(h, y, step, memory))]
         if self.ffn is not None:
-            self._sublayer(x, self.ffn_norm, self.extra.get("ffn_scale"), lambda h, y: self.ffn.forward(h, y, step))
-        for name, part in self.extra.items():
-            if name.startswith("after"):
-                part.forward(ops.cast_rows(x, part.rt.dtype), x, step)
+            subs.append((self.ffn_norm, self.extra.get("ffn_scale"), lambda h, y: self.ffn.forward(h, y, step)))
+        after = [part for name, part in self.extra.items() if name.startswith("after")]
+        # one matrix of 32-bit rows that every sublayer adds into, and one copy of the stream in the activation type: the
+        # pass that joins a sublayer's output to the stream zeroes the first and renews the second for the next reader
+        y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        h = ops.cast_rows(x, dt, zero=y)
+        for i, (norm, scale, run) in enumerate(subs):
+            run(h, y)
+            more, reader = i + 1 < len(subs), i + 1 < len(subs) or bool(after)
+            norm.add_normed(x, y, scale.weight if scale is not None else None, cast_out=h if (low and reader) else None, zero_y=more)
+        for i, part in enumerate(after):
+            part.forward(h, x, step)
+            if low and i + 1 < len(after):
+                h = ops.cast_rows(x, dt)

@@ -48,10 +48,12 @@ class RmsNorm(Norm):
             return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)
 
 
-    def add_normed(self, x: torch.Tensor, y: torch.Tensor, scale: Optional[torch.Tensor] = None) -> None:
-        """x += y / sqrt(mean(y^2) + eps) * w [* scale]: the norm on a sublayer's output, joined to the stream in one pass."""
+    def add_normed(self, x: torch.Tensor, y: torch.Tensor, scale: Optional[torch.Tensor] = None,
+                   cast_out: Optional[torch.Tensor] = None, zero_y: bool = False) -> None:
+        """x += y / sqrt(mean(y^2) + eps) * w [* scale]: the norm on a sublayer's output, joined to the stream in one pass;
+        the same pass can leave the new stream in the activation type in `cast_out` and y zeroed, for the next sublayer."""
         with ops.bucket("norm"):
-            ops.postnorm_add(x, y, self.weight32, self.eps, scale)
+            ops.postnorm_add(x, y, self.weight32, self.eps, scale, cast_out=cast_out, zero_y=zero_y)
 
 
 @register("norm", "channel_scale")

@@ -158,6 +158,39 @@ def prompt_then_tokens(eng, t, cut, graph=None):
 
 PATHS = [("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"), ("C", "bfloat16")]
 
+# ---- the row kernels of a layer that norms what it adds, against 64-bit torch ---------------------------------------------
+@pytest.mark.parametrize("rows,width", [(5, 52), (3, 96), (70, 1028), (2, 7)])
+def test_norm_on_a_sublayers_output_with_the_next_input_and_a_zeroed_sum(rows, width):
+    from ghost_infer_b200.kernels import ops
+    g = torch.Generator(device="cuda:0").manual_seed(rows * 1000 + width)
+    x = torch.randn((rows, width), device="cuda:0", generator=g)
+    y = torch.randn((rows, width), device="cuda:0", generator=g) * 3.0
+    w = torch.rand((width,), device="cuda:0", generator=g) + 0.5
+    sc = torch.rand((width,), device="cuda:0", generator=g) * 2.0
+    eps = 1e-5
+    ref = x.double() + y.double() / torch.sqrt((y.double() ** 2).mean(-1, keepdim=True) + eps) * w.double() * sc.double()
+    for low in (True, False):
+        xs, ys = x.clone(), y.clone()
+        h = torch.full((rows, width), 7.0, device="cuda:0", dtype=torch.bfloat16 if low else torch.float32)
+        ops.postnorm_add(xs, ys, w, eps, sc, cast_out=h, zero_y=True)
+        torch.testing.assert_close(xs.double(), ref, rtol=1e-5, atol=1e-5)
+        assert float(ys.abs().max()) == 0.0
+        assert torch.equal(h, xs.to(h.dtype))                    # the next reader gets the new stream, rounded once
+    xs, ys = x.clone(), y.clone()
+    ops.postnorm_add(xs, ys, w, eps)                             # no scale, nothing else written
+    ref1 = x.double() + y.double() / torch.sqrt((y.double() ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    torch.testing.assert_close(xs.double(), ref1, rtol=1e-5, atol=1e-5)
+    assert torch.equal(ys, y)
+    z = torch.full((rows, width), 3.0, device="cuda:0")
+    hb = ops.cast_rows(x, torch.bfloat16, zero=z)
+    assert torch.equal(hb, x.to(torch.bfloat16)) and float(z.abs().max()) == 0.0
+    assert torch.equal(ops.cast_rows(x, torch.bfloat16), x.to(torch.bfloat16))
+    a = torch.randn((rows, width), device="cuda:0", generator=g)
+    out = x.clone()
+    ops.axpy(out, a, 1.3)
+    torch.testing.assert_close(out.double(), x.double() + 1.3 * a.double(), rtol=1e-6, atol=1e-6)
+
+
 # ---- each mechanism alone: one- and two-layer models ------------------------------------------------------------------
 ALONE = {
     "window": [layer("attention", att(3, 1, 8, 12, 0.4, 7, 8))],
