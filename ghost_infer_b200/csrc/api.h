@@ -456,11 +456,12 @@ int gi_act_rows(void* out, const void* in, long ld_in, int dtype, int n_rows, in
 // ---- linear attention with a matrix of state per head (linear_state.cu) -------------------------------------------------
 // o float32 [tokens, heads * V].  q, k: rows with qk_heads * K numbers at the pointer; v: heads * V.  a_in / b_in: rows with
 // one number per head (null: a constant decay decay_c[h] / no write strength).  With a_in, decay_c holds A_log.
+// n_tokens: the rows of the step (0: not known); as many as sequences means one token each, and a smaller kernel runs.
 int gi_linear_state(float* o, const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const void* a_in,
                     long lda, const void* b_in, long ldb, int dtype, const float* decay_c, const float* dt_bias, float* state,
                     long state_ld, int state_rows, const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads,
                     int qk_heads, int K, int V, int in_act, int unit_norm, float norm_eps, float q_scale, int delta,
-                    void* stream);
+                    int n_tokens, void* stream);
 
 #ifdef __cplusplus
 }

@@ -85,9 +85,11 @@ struct LsArgs {
 // tokens per chunk: two buffers of it stay under 48 KB of shared memory
 template <int KR> struct LsChunk { static constexpr int value = KR >= 32 ? 8 : 16; };
 
-template <typename T, int KR, int COLS, bool DELTA>
-// two blocks an SM for the narrower tiles: a grid of about as many blocks as SMs times two then runs as one round
-__global__ void __launch_bounds__(COLS * LS_LANES + LS_PREP, COLS <= 16 ? 2 : 1)
+// WALK: the step holds sequences of many tokens, and eight whole tokens run without a test between them; without it (steps
+// of one token a sequence) the kernel is the same but smaller, so that two blocks fit an SM at every tile width.
+// Two blocks an SM for the narrower tiles too: a grid of about as many blocks as SMs times two then runs as one round.
+template <typename T, int KR, int COLS, bool DELTA, bool WALK>
+__global__ void __launch_bounds__(COLS * LS_LANES + LS_PREP, (COLS <= 16 || !WALK) ? 2 : 1)
 linear_state_kernel(const LsArgs a) {
   constexpr int Kp = KR * LS_LANES;            // rows with padding
   constexpr int M = KR / 4;                    // groups of four rows per lane; also a preparing lane's share of a row
@@ -320,7 +322,7 @@ linear_state_kernel(const LsArgs a) {
     };
     for (int t0 = 0; t0 < n; t0 += LS_TB) {
       float acc[LS_TB];
-      if (t0 + LS_TB <= n) {     // eight whole tokens: nothing to test between them, so the next one's loads start early
+      if (WALK && t0 + LS_TB <= n) {     // eight whole tokens: nothing to test between them, so the next one's loads start early
 #pragma unroll
         for (int tl = 0; tl < LS_TB; ++tl) token(t0 + tl, acc[tl]);
       } else {
@@ -363,22 +365,25 @@ int ls_sm_count() {
 }
 
 template <typename T, int KR, int COLS>
-cudaError_t ls_launch(const LsArgs& a, int n_seqs, bool delta, cudaStream_t stream) {
+cudaError_t ls_launch(const LsArgs& a, int n_seqs, bool delta, bool walk, cudaStream_t stream) {
   constexpr int CH = LsChunk<KR>::value;
   const size_t smem = 2 * (size_t)(2 * CH * KR * LS_LANES + 2 * CH * COLS + 2 * CH) * sizeof(float);
   const dim3 grid(a.heads, n_seqs, (a.V + COLS - 1) / COLS), block(COLS * LS_LANES + LS_PREP);
-  return delta ? gi::launch(linear_state_kernel<T, KR, COLS, true>, grid, block, smem, stream, a)
-               : gi::launch(linear_state_kernel<T, KR, COLS, false>, grid, block, smem, stream, a);
+  if (walk)
+    return delta ? gi::launch(linear_state_kernel<T, KR, COLS, true, true>, grid, block, smem, stream, a)
+                 : gi::launch(linear_state_kernel<T, KR, COLS, false, true>, grid, block, smem, stream, a);
+  return delta ? gi::launch(linear_state_kernel<T, KR, COLS, true, false>, grid, block, smem, stream, a)
+               : gi::launch(linear_state_kernel<T, KR, COLS, false, false>, grid, block, smem, stream, a);
 }
 
 template <typename T, int KR>
-cudaError_t ls_pick_tile(const LsArgs& a, int n_seqs, bool delta, cudaStream_t stream) {
+cudaError_t ls_pick_tile(const LsArgs& a, int n_seqs, bool delta, bool walk, cudaStream_t stream) {
   // the widest tile that still gives every SM a block: with fewer blocks than SMs the token-by-token walk, whose length a
   // block cannot shorten, runs on a part of the device only
   const long per = (long)a.heads * n_seqs, sms = ls_sm_count();
-  if (per * ((a.V + 31) / 32) >= sms || a.V <= 8) return ls_launch<T, KR, 32>(a, n_seqs, delta, stream);
-  if (per * ((a.V + 15) / 16) >= sms) return ls_launch<T, KR, 16>(a, n_seqs, delta, stream);
-  return ls_launch<T, KR, 8>(a, n_seqs, delta, stream);
+  if (per * ((a.V + 31) / 32) >= sms || a.V <= 8) return ls_launch<T, KR, 32>(a, n_seqs, delta, walk, stream);
+  if (per * ((a.V + 15) / 16) >= sms) return ls_launch<T, KR, 16>(a, n_seqs, delta, walk, stream);
+  return ls_launch<T, KR, 8>(a, n_seqs, delta, walk, stream);
 }
 
 }  // namespace
@@ -387,7 +392,7 @@ extern "C" int gi_linear_state(float* o, const void* q, long ldq, const void* k,
                                const void* a_in, long lda, const void* b_in, long ldb, int dtype, const float* decay_c,
                                const float* dt_bias, float* state, long state_ld, int state_rows, const int* cu_seqlens,
                                const int* seq_slots, int n_seqs, int heads, int qk_heads, int K, int V, int in_act,
-                               int unit_norm, float norm_eps, float q_scale, int delta, void* stream) {
+                               int unit_norm, float norm_eps, float q_scale, int delta, int n_tokens, void* stream) {
   if (n_seqs <= 0) return GI_OK;
   if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || K <= 0 || V <= 0)
     return gi::fail(GI_ERR_ARG, "linear_state: bad sizes (heads %d, query/key heads %d, keys %d, values %d)", heads, qk_heads, K, V);
@@ -411,12 +416,14 @@ extern "C" int gi_linear_state(float* o, const void* q, long ldq, const void* k,
     a.vec_in = (K % vw == 0 && V % vw == 0 && ldq % vw == 0 && ldk % vw == 0 && ldv % vw == 0 &&
                 (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && esz * vw == 16) ? 1 : 0;
   }
+  // more tokens than sequences: some sequence brings several, the step is a prompt step (n_tokens 0: not known)
+  const bool walk = n_tokens <= 0 || n_tokens > n_seqs;
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T, {
-    if (K <= 4 * LS_LANES) e = ls_pick_tile<T, 4>(a, n_seqs, delta != 0, (cudaStream_t)stream);
-    else if (K <= 8 * LS_LANES) e = ls_pick_tile<T, 8>(a, n_seqs, delta != 0, (cudaStream_t)stream);
-    else if (K <= 16 * LS_LANES) e = ls_pick_tile<T, 16>(a, n_seqs, delta != 0, (cudaStream_t)stream);
-    else e = ls_pick_tile<T, 32>(a, n_seqs, delta != 0, (cudaStream_t)stream);
+    if (K <= 4 * LS_LANES) e = ls_pick_tile<T, 4>(a, n_seqs, delta != 0, walk, (cudaStream_t)stream);
+    else if (K <= 8 * LS_LANES) e = ls_pick_tile<T, 8>(a, n_seqs, delta != 0, walk, (cudaStream_t)stream);
+    else if (K <= 16 * LS_LANES) e = ls_pick_tile<T, 16>(a, n_seqs, delta != 0, walk, (cudaStream_t)stream);
+    else e = ls_pick_tile<T, 32>(a, n_seqs, delta != 0, walk, (cudaStream_t)stream);
   });
   return gi::check(e, "linear_state");
 }

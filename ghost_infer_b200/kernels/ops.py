@@ -112,7 +112,7 @@ def _bind():
         "gi_norm_gate": [P, I, P, P, L, P, I, I, I, I, I, I, F, P],
         "gi_side_gate": [P, P, L, I, P, L, I, P, I, I, I, P],
         "gi_act_rows": [P, P, L, I, I, I, P],
-        "gi_linear_state": [P, P, L, P, L, P, L, P, L, P, L, I, P, P, P, L, I, P, P, I, I, I, I, I, I, I, F, F, I, P],
+        "gi_linear_state": [P, P, L, P, L, P, L, P, L, P, L, I, P, P, P, L, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -2060,5 +2060,5 @@ def linear_state(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch
         o.data_ptr(), q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), ptr(decay_in), ldo(decay_in),
         ptr(beta_in), ldo(beta_in), _dt(q, "queries"), decay.data_ptr(), ptr(dt_bias), state.data_ptr(), state.stride(0),
         state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads, qk_heads, key_dim,
-        v_dim, int(in_act), int(unit_norm), float(norm_eps), float(q_scale), int(delta), _stream()))
+        v_dim, int(in_act), int(unit_norm), float(norm_eps), float(q_scale), int(delta), int(n), _stream()))
     return o
