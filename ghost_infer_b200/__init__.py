@@ -18,11 +18,14 @@ from .config.nuzinex import NuzinexConfig, build_nuzinex_spec
 register_architecture("Barovik", BarovikConfig.from_dict, build_barovik_spec, replace=True)
 register_architecture("Nuzinex", NuzinexConfig.from_dict, build_nuzinex_spec, replace=True)
 register_architecture("Navalorn", NavalornConfig.from_dict, build_navalorn_spec, replace=True)
+from .config.torutar import TorutarConfig, build_torutar_spec
+
+register_architecture("Torutar", TorutarConfig.from_dict, build_torutar_spec, replace=True)
 
 from .engine import Engine, Model, StepEntry  # noqa: E402
 from .api import LLM  # noqa: E402
 from .sampling import SamplingParams  # noqa: E402
 
-__all__ = ["ConfigError", "LlamaConfig", "BarovikConfig", "NavalornConfig", "NuzinexConfig", "UnknownArchitectureError", "load_config", "register_architecture",
+__all__ = ["ConfigError", "LlamaConfig", "BarovikConfig", "NavalornConfig", "NuzinexConfig", "TorutarConfig", "UnknownArchitectureError", "load_config", "register_architecture",
            "registered_architectures", "Engine", "Model", "StepEntry", "LLM", "SamplingParams"]
 __version__ = "0.1.0"

@@ -35,13 +35,15 @@ class CacheRequest:
     kind "window": only the last `window` positions are ever read again; kind "chunk": only positions p with
     floor(p / window) equal to that of the reader's own position.  `v_head_dim`: the values' width when it is not
     the keys' `head_dim`.  `values_in_keys`: nothing is stored for the values; a position's value is the leading
-    `v_head_dim` numbers of its key row (a latent that serves as both), and `LayerMemory.v` is None."""
+    `v_head_dim` numbers of its key row (a latent that serves as both), and `LayerMemory.v` is None.  `keep_first`: a
+    window cache also keeps the sequence's first so many positions for good."""
     kind: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     values_in_keys: bool = False
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "window", "chunk"):
@@ -50,6 +52,8 @@ class CacheRequest:
             raise ValueError(f"a {self.kind} cache needs a positive size")
         if self.v_head_dim is not None and self.v_head_dim < 1:
             raise ValueError("the values' width must be positive")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise ValueError("only a window cache keeps first positions, and not a negative number of them")
         if self.values_in_keys and self.value_dim > self.head_dim:
             raise ValueError("values that live in the key rows cannot be wider than the keys")
 
@@ -75,6 +79,7 @@ class LayerMemory:
     writes: bool                          # False when the entry reads another entry's memory
     state: Optional[torch.Tensor]         # [max_slots + 1, *shape] or None; the last row (slot -1) is for padding rows
     chunk: Optional[int] = None           # size of the chunks of a "chunk" group
+    block_state: Optional[torch.Tensor] = None   # the same kind of memory for the layer's arrangement itself (always the entry's own)
 
 
 class _Group:
@@ -109,7 +114,7 @@ class SequenceCache:
                  *, max_tokens: int, max_slots: int, max_seq_len: int, dtype: torch.dtype,
                  device: torch.device | str = "cpu"):
         """`requests`: one tuple per schedule entry: (entry index, cache request or None,
-        state request or None, memory_of or None)."""
+        state request or None, memory_of or None[, state request of the layer's arrangement or None])."""
         if max_tokens < 1:
             raise ValueError("max_tokens must be positive")
         self.device = torch.device(device)
@@ -117,7 +122,7 @@ class SequenceCache:
         self.max_tokens = int(max_tokens)
         self.n_pages = pages_for(max_tokens)
         # a sequence whose every position stays cached cannot be longer than the pool; one that only keeps windows can
-        keeps_all = any(creq is not None and creq.kind == "full" and memory_of is None for _, creq, _, memory_of in requests)
+        keeps_all = any(r[1] is not None and r[1].kind == "full" and r[3] is None for r in requests)
         self.max_seq_len = int(min(max_seq_len, self.n_pages * PAGE_TOKENS)) if keeps_all else int(max_seq_len)
         self.max_pages_per_seq = pages_for(self.max_seq_len)
         self.slots = SlotAllocator(max_slots)
@@ -127,8 +132,12 @@ class SequenceCache:
         self._group_of_entry: Dict[int, Tuple[_Group, int]] = {}
         self._reads_from: Dict[int, int] = {}
         self._state: Dict[int, torch.Tensor] = {}
+        self._block_state: Dict[int, torch.Tensor] = {}
         by_request: Dict[CacheRequest, _Group] = {}
-        for entry, creq, sreq, memory_of in requests:
+        requests = [tuple(r) + (None,) * (5 - len(r)) for r in requests]
+        for entry, creq, sreq, memory_of, breq in requests:
+            if breq is not None:      # an arrangement's own state is never borrowed: an entry that reads another's cache keeps its own
+                self._block_state[entry] = torch.zeros((max_slots + 1,) + tuple(breq.shape), dtype=breq.dtype, device=self.device)
             if memory_of is not None:
                 self._reads_from[entry] = memory_of
                 continue
@@ -157,7 +166,7 @@ class SequenceCache:
         return total
 
     def state_bytes_per_sequence(self) -> int:
-        return sum(t[0].numel() * t.element_size() for t in self._state.values())
+        return sum(t[0].numel() * t.element_size() for d in (self._state, self._block_state) for t in d.values())
 
     @property
     def free_pages(self) -> int:
@@ -174,8 +183,9 @@ class SequenceCache:
         for g in self._groups:
             g.pages[s] = []
             g.first_live[s] = 0
-        for t in self._state.values():
-            t[s].zero_()
+        for d in (self._state, self._block_state):
+            for t in d.values():
+                t[s].zero_()
         return s
 
     def close_slot(self, slot: int) -> None:
@@ -229,7 +239,8 @@ class SequenceCache:
                 dead_before = ((new_len // g.request.window) * g.request.window) // PAGE_TOKENS
             else:
                 continue
-            first = g.first_live[slot]
+            # a window that keeps first positions never gives back the pages they lie in
+            first = max(g.first_live[slot], pages_for(g.request.keep_first)) if g.request.kind == "window" else g.first_live[slot]
             if dead_before > first:
                 pages = g.pages[slot]
                 g.pool.give_back([pages[i] for i in range(first, dead_before)])
@@ -249,8 +260,9 @@ class SequenceCache:
             g.first_live[slot] = 0
             g.table_host[slot, :] = 0
             g.dirty.pop(slot, None)
-        for t in self._state.values():
-            t[slot].zero_()
+        for d in (self._state, self._block_state):
+            for t in d.values():
+                t[slot].zero_()
         self.lengths[slot] = 0
 
     def truncate(self, slot: int, pos: int) -> int:
@@ -260,7 +272,7 @@ class SequenceCache:
         cur = self.lengths[slot]
         if pos >= cur:
             return cur
-        if self._state or any(g.request.kind in ("window", "chunk") and g.first_live[slot] * PAGE_TOKENS > 0 for g in self._groups):
+        if self._state or self._block_state or any(g.request.kind in ("window", "chunk") and g.first_live[slot] * PAGE_TOKENS > 0 for g in self._groups):
             return cur
         for g in self._groups:
             keep = pages_for(pos)
@@ -308,8 +320,9 @@ class SequenceCache:
         writes = entry not in self._reads_from
         gi = self._group_of_entry.get(src)
         state = self._state.get(src)
+        block_state = self._block_state.get(entry)
         if gi is None:
-            return LayerMemory(None, None, None, None, writes, state)
+            return LayerMemory(None, None, None, None, writes, state, None, block_state)
         g, idx = gi
         return LayerMemory(g.k[idx], g.v[idx] if g.v is not None else None, g.table_dev, g.request.window if g.request.kind == "window" else None,
-                           writes, state, g.request.window if g.request.kind == "chunk" else None)
+                           writes, state, g.request.window if g.request.kind == "chunk" else None, block_state)

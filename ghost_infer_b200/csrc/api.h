@@ -463,6 +463,82 @@ int gi_linear_state(float* o, const void* q, long ldq, const void* k, long ldk, 
                     int qk_heads, int K, int V, int in_act, int unit_norm, float norm_eps, float q_scale, int delta,
                     int n_tokens, void* stream);
 
+// The same with the gates ready made: g_direct / u_direct float32 [tokens, heads] (either may be null) give the decay of every
+// token and head as it is, and a number that multiplies what the token writes (S <- g S + k (u v)^T; not with the delta rule).
+int gi_linear_state_gated(float* o, const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const void* a_in,
+                          long lda, const void* b_in, long ldb, int dtype, const float* decay_c, const float* dt_bias,
+                          const float* g_direct, const float* u_direct, float* state, long state_ld, int state_rows,
+                          const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads, int qk_heads, int K, int V, int in_act,
+                          int unit_norm, float norm_eps, float q_scale, int delta, int n_tokens, void* stream);
+
+// ---- a matrix memory with a running maximum (mlstm.cu) ------------------------------------------------------------------
+// Per token and head: keep = exp(f + m_prev - m), put = exp(i - m), out_scale = s / (max(|n . (s q)|, exp(-m)) + 1e-6), with
+// i = cap tanh((gate_i + bias_i) / cap), f = log sigmoid(cap tanh((gate_f + bias_f) / cap)), m = max(f + m_prev, i),
+// n = keep n_prev + put k.  q, k: rows with heads * K numbers at the pointer; gate_i, gate_f: rows with one number per head.
+// state: per slot and head K + 1 floats (n, m) at the pointer, rows state_ld apart; the last of state_rows rows serves slot -1.
+int gi_mlstm_gates(float* keep, float* put, float* out_scale, const void* q, long ldq, const void* k, long ldk, const void* gate_i,
+                   const void* gate_f, long ldg, int dtype, const float* bias_i, const float* bias_f, float cap, float q_scale,
+                   float* state, long state_ld, int state_rows, const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads,
+                   int K, void* stream);
+
+// ---- several copies of the residual stream (hyper_streams.cu) -----------------------------------------------------------
+// x float32 [tokens][streams][d].
+int gi_stream_expand(float* x, const float* e, int n_tokens, int streams, int d, void* stream);
+// out[r] = sum over the copies of x[rows[r]] (rows null: every token in order).
+int gi_stream_sum(float* out, const float* x, const int* rows, int n_rows, int streams, int d, void* stream);
+// h[t] = rmsnorm(sum_s blend[s] x[t][s]) * w in `dtype`; `zero` (or null): float32 [tokens][d] set to zero in the same pass.
+int gi_hyper_read(void* h, int dtype, const float* x, const float* blend, const void* w, int w_dtype, float* zero, int n_tokens,
+                  int streams, int d, float eps, void* stream);
+// out[t] = h[t] + sum_j taps_w[:, j] h[t - taps + 1 + j] per channel (taps_w [d][taps]); inputs before the step come from the
+// sequence's state (float32 [taps - 1][d] per slot, oldest first; rows state_ld apart, the last row serves slot -1).  Rows of
+// one sequence are neighbours in the step and carry the same slot.
+int gi_input_conv(void* out, const void* h, int dtype, const void* taps_w, int w_dtype, const float* state, long state_ld,
+                  int state_rows, const int* slots, int n_tokens, int d, int taps, void* stream);
+// x[t][to] = sum_s mix[s][to] x[t][s] + share[to] * y[t] * sigmoid(z[t] + z_bias) (z null: no gate); with `state`, the block of
+// a sequence's last token renews the convolution's state from `h` (the rows input_conv read).
+int gi_hyper_write(float* x, const float* y, const void* z, const void* z_bias, int dtype, int w_dtype, const float* mix,
+                   const float* share, const void* h, float* state, long state_ld, int state_rows, const int* slots, int n_tokens,
+                   int streams, int d, int taps, void* stream);
+int gi_scale_rows(float* x, float c, long n_values, void* stream);
+
+// ---- attention normed head by head, gated heads, clamped gated rows (head_parts.cu) -------------------------------------
+// One token's float32 row [q: n_heads * hd | k: n_kv * hd | v: n_kv * hdv | ...] (n_kv 0: queries only): biases (each may be
+// null), per-head RMS norms of q and k with weights wq / wk of hd numbers shared by the heads (norm_q / norm_k; a null weight
+// is 1), per-head RMS norm of v without a weight (norm_v), rotation as in gi_qk_prepare, q into q_out, k and v into the pages.
+int gi_head_prepare(void* q_out, long ldq, int dtype, const float* in, long ld, const void* bq, const void* bk, const void* bv,
+                    const void* wq, const void* wk, int w_dtype, int norm_q, int norm_k, int norm_v, float eps, const float* table,
+                    int half, int adjacent, const int* positions, const int* slots, const int* block_table, int max_pages,
+                    void* kcache, void* vcache, int n_tokens, int n_heads, int n_kv, int hd, int hdv, void* stream);
+// out[t][h][:] = a[t][h][:] * sigmoid(g[t * ldg + h]).
+int gi_head_gate(void* out, const void* a, int dtype, const float* g, long ldg, int n_rows, int n_heads, int hdv, void* stream);
+// v = y[t][h][:] * scale[t][h] (scale null: 1); out = v / sqrt(mean(v^2) + eps) * w[h][:] * sigmoid(g[t * ldg + h * hdv + :]).
+int gi_scaled_norm_gate(void* out, int dtype, const float* y, const float* scale, const float* g, long ldg, const void* w, int w_dtype,
+                        int n_rows, int n_heads, int hdv, float eps, void* stream);
+// rows [gate: f | up: f] -> min(gate, limit) * sigmoid(alpha * that) * (clamp(up, -limit, limit) + 1); limit <= 0: no clamps.
+int gi_clamped_glu(void* out, const void* in, long ld_in, int dtype, int n_rows, int f, float limit, float alpha, void* stream);
+
+// ---- additions to the routed feed-forward and the plain attention -------------------------------------------------------
+// score_mode 2: shares = softmax over ALL experts; the `top` largest of share + correction (null: 0) are chosen; weights =
+// the chosen shares / (their sum + 1e-20) * weight_scale.
+int gi_moe_route_shares(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
+                        const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, int score_mode,
+                        const float* correction, float weight_scale, void* stream);
+// gi_moe_gemm_gate_up with the clamped form of the gated value for limit > 0 (see gi_clamped_glu).
+int gi_moe_gemm_gate_up_clamped(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
+                                const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
+                                int interleaved, float limit, float alpha, void* stream);
+// The plain attention kernels with a window that keeps the sequence's first `keep_first` positions visible as well.
+int gi_attn_prefill_generic_ex3(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                                const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,
+                                const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads,
+                                int n_kv, int hd, float scale, int window, int hdv, float softcap, const float* sinks,
+                                int chunk, long v_row_stride, int keep_first, void* stream);
+int gi_attn_decode_generic_ex3(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, int dtype,
+                               const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                               const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                               float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
+                               const float* sinks, int chunk, long v_row_stride, int keep_first, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

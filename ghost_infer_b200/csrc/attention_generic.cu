@@ -31,7 +31,7 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
                     const T* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                     const int* __restrict__ seq_pos0, int n_heads, int n_kv, int hd, float scale, int window,
-                    int hdv, float softcap, const float* __restrict__ sinks, int chunk, long vrs) {
+                    int hdv, float softcap, const float* __restrict__ sinks, int chunk, long vrs, int keep_first) {
   extern __shared__ float smem[];
   const int ldk = hd + 1, ldv = hdv + 1;
   float* Qs = smem;                  // [QT][hd+1]
@@ -60,27 +60,31 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
   if (chunk > 0) t_first = max(t_first, ((pos0 + q0) / chunk) * chunk);
   const int t_begin = (t_first / KT) * KT;
   const int c_row = chunk > 0 ? p_row / chunk : 0;
+  // a window may keep the sequence's first `keep_first` positions visible: their tiles come before the window's own
+  const int kept = window > 0 ? keep_first : 0;
+  const int kept_end = min(((kept + KT - 1) / KT) * KT, t_begin);
 
   float m = -INFINITY, l = 0.f;
   float acc[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
 
-  for (int kt = t_begin; kt <= p_last; kt += KT) {
+  for (int kt = kept_end > 0 ? 0 : t_begin; kt <= p_last; kt += KT) {
+    if (kt == kept_end && kept_end > 0 && kt < t_begin) kt = t_begin;
     __syncthreads();
     const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (kt % PAGE_TOKENS);
     const size_t base = row0 * hd, base_v = row0 * (size_t)vrs;
     for (int idx = tid; idx < KT * hd; idx += 128) {
       const int j = idx / hd, d = idx % hd;
-      const bool live = kt + j <= p_last && kt + j >= t_first;   // rows no query here sees are not read
+      const bool live = kt + j <= p_last && (kt + j >= t_first || kt + j < kept);   // rows no query here sees are not read
       Ks[j * ldk + d] = live ? gi::ldf(kcache + base + (size_t)j * hd + d) : 0.f;
       if (hdv == hd) Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
     }
     if (hdv != hd) {
       for (int idx = tid; idx < KT * hdv; idx += 128) {
         const int j = idx / hdv, d = idx % hdv;
-        const bool live = kt + j <= p_last && kt + j >= t_first;
+        const bool live = kt + j <= p_last && (kt + j >= t_first || kt + j < kept);
         Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
       }
     }
@@ -95,7 +99,7 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
       const float* qr = Qs + row * ldk;
       const float* kr = Ks + j * ldk;
       for (int d = 0; d < hd; ++d) dot = fmaf(qr[d], kr[d], dot);
-      const bool ok = row_ok && t <= p_row && (window <= 0 || t > p_row - window) && (chunk <= 0 || t / chunk == c_row);
+      const bool ok = row_ok && t <= p_row && (window <= 0 || t > p_row - window || t < kept) && (chunk <= 0 || t / chunk == c_row);
       float sc = dot * scale;
       if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
       s[jj] = ok ? sc : -INFINITY;
@@ -164,7 +168,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
                    const T* __restrict__ q, long ldq, const T* __restrict__ kcache, const T* __restrict__ vcache,
                    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slots,
                    const int* __restrict__ seq_lens, int n_heads, int n_kv, int hd, float scale, int window,
-                   int n_splits, int own_tiles, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk, long vrs) {
+                   int n_splits, int own_tiles, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk, long vrs, int keep_first) {
   extern __shared__ float smem[];
   float* Qs = smem;                       // [GC][hd]
   float* Mo = Qs + GC * hd;               // [4][GC][hdv] warp outputs
@@ -190,7 +194,10 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
   if (window > 0) t_first = max(0, len - window);
   if (pos_chunk > 0) t_first = max(t_first, ((len - 1) / pos_chunk) * pos_chunk);
   const int t_base = (t_first / KT) * KT;
-  const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
+  // a window may keep the sequence's first `keep_first` positions visible: their tiles are counted before the window's own
+  const int kept = window > 0 ? keep_first : 0;
+  const int kept_tiles = min((kept + KT - 1) / KT, t_base / KT);
+  const int tiles = kept_tiles + (len > t_base ? (len - t_base + KT - 1) / KT : 0);
   // own_tiles > 0: a slice is that many tiles of the sequence's own span, so its sums do not depend on what else
   // the launch holds (slices past the span stay empty); else the span is cut into n_splits equal slices
   const int per = own_tiles > 0 ? own_tiles : (tiles + n_splits - 1) / n_splits;
@@ -206,12 +213,12 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
   }
 
   for (int tile = tile_lo + warp; tile < tile_hi; tile += 4) {
-    const int t0 = t_base + tile * KT;
+    const int t0 = tile < kept_tiles ? tile * KT : t_base + (tile - kept_tiles) * KT;
     const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + t0 / PAGE_TOKENS] : 0;
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS);
     const size_t base = row0 * hd, base_v = row0 * (size_t)vrs;
     const int t = t0 + lane;
-    const bool ok = t < len && t >= t_first;
+    const bool ok = t < len && (t >= t_first || t < kept);
     float s[GC];
 #pragma unroll
     for (int g = 0; g < GC; ++g) s[g] = 0.f;
@@ -244,7 +251,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 #pragma unroll
       for (int c = 0; c < DC; ++c) {
         const int d = lane + 32 * c;
-        v[c] = (d < hdv && t0 + j >= t_first) ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
+        v[c] = (d < hdv && (t0 + j >= t_first || t0 + j < kept)) ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
       }
 #pragma unroll
       for (int g = 0; g < GC; ++g) {
@@ -381,7 +388,7 @@ template <typename T>
 int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, const T* q, long ldq,
                    const T* kc, const T* vc, const int* bt, int max_pages, const int* cu, const int* slots,
                    const int* pos0, int H, int KV, int hd, float scale, int window, int hdv, float softcap,
-                   const float* sinks, int chunk, long vrs) {
+                   const float* sinks, int chunk, long vrs, int keep_first) {
 #define GI_PREFILL_CASE(D)                                                                                       \
   case D: {                                                                                                      \
     auto kern = attn_prefill_kernel<T, D>;                                                                       \
@@ -389,7 +396,7 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill: %s", cudaGetErrorString(e));        \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window, hdv, softcap, sinks, chunk, vrs); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window, hdv, softcap, sinks, chunk, vrs, keep_first); \
     break;                                                                                                       \
   }
   switch (dpt) {
@@ -410,7 +417,7 @@ template <typename T, int GC>
 int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, float* po, float* pml,
                      const T* q, long ldq, const T* kc, const T* vc, const int* bt, int max_pages, const int* slots,
                      const int* lens, int H, int KV, int hd, float scale, int window, int n_splits, int own_tiles,
-                     int hdv, float softcap, const float* sinks, int chunk, long vrs) {
+                     int hdv, float softcap, const float* sinks, int chunk, long vrs, int keep_first) {
 #define GI_DECODE_CASE(D)                                                                                        \
   case D: {                                                                                                      \
     auto kern = attn_decode_kernel<T, GC, D>;                                                                    \
@@ -418,7 +425,7 @@ int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, lon
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));         \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, vrs); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, vrs, keep_first); \
     break;                                                                                                       \
   }
   switch (dc) {
@@ -476,7 +483,19 @@ extern "C" int gi_attn_prefill_generic_ex2(void* out, long ldo, const void* q, l
                                            int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
                                            int hdv, float softcap, const float* sinks, int chunk, long v_row_stride,
                                            void* stream) {
+  return gi_attn_prefill_generic_ex3(out, ldo, q, ldq, dtype, kcache, vcache, block_table, max_pages, cu_seqlens, seq_slots,
+                                     seq_pos0, n_seqs, max_q_len, n_heads, n_kv, hd, scale, window, hdv, softcap, sinks, chunk,
+                                     v_row_stride, 0, stream);
+}
+
+extern "C" int gi_attn_prefill_generic_ex3(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                                           const void* vcache, const int* block_table, int max_pages,
+                                           const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                           int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
+                                           int hdv, float softcap, const float* sinks, int chunk, long v_row_stride,
+                                           int keep_first, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return gi::fail(GI_ERR_ARG, "attention: kept first positions go with a window, not with chunks");
   if (hdv <= 0 || hdv > 512) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..512", hdv);
   if (v_row_stride < hdv) return gi::fail(GI_ERR_ARG, "attention: value rows %ld apart cannot hold %d values", v_row_stride, hdv);
   if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
@@ -491,7 +510,7 @@ extern "C" int gi_attn_prefill_generic_ex2(void* out, long ldo, const void* q, l
   GI_DISPATCH_DTYPE(dtype, T,
       return (launch_prefill<T>(dpt, grid, smem, (cudaStream_t)stream, (T*)out, ldo, (const T*)q, ldq, (const T*)kcache,
                                 (const T*)vcache, block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv,
-                                hd, scale, window, hdv, softcap, sinks, chunk, v_row_stride)));
+                                hd, scale, window, hdv, softcap, sinks, chunk, v_row_stride, keep_first)));
   return GI_OK;
 }
 
@@ -522,7 +541,19 @@ extern "C" int gi_attn_decode_generic_ex2(void* out, long ldo, float* part_o, fl
                                           int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
                                           int own_tiles, int hdv, float softcap, const float* sinks, int chunk,
                                           long v_row_stride, void* stream) {
+  return gi_attn_decode_generic_ex3(out, ldo, part_o, part_ml, q, ldq, dtype, kcache, vcache, block_table, max_pages, seq_slots,
+                                    seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks,
+                                    chunk, v_row_stride, 0, stream);
+}
+
+extern "C" int gi_attn_decode_generic_ex3(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                          int dtype, const void* kcache, const void* vcache, const int* block_table,
+                                          int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs,
+                                          int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                          int own_tiles, int hdv, float softcap, const float* sinks, int chunk,
+                                          long v_row_stride, int keep_first, void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return gi::fail(GI_ERR_ARG, "attention: kept first positions go with a window, not with chunks");
   if (hdv <= 0 || hdv > 512) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..512", hdv);
   if (v_row_stride < hdv) return gi::fail(GI_ERR_ARG, "attention: value rows %ld apart cannot hold %d values", v_row_stride, hdv);
   if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
@@ -546,7 +577,7 @@ extern "C" int gi_attn_decode_generic_ex2(void* out, long ldo, float* part_o, fl
     GI_DISPATCH_DTYPE(dtype, T,                                                                                    \
         rc = (launch_decode_dc<T, G>(dc, grid, smem, s, (T*)out, ldo, part_o, part_ml, (const T*)q, ldq, (const T*)kcache, \
                                      (const T*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, hd, \
-                                     scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, v_row_stride))); \
+                                     scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, v_row_stride, keep_first))); \
     break;
   switch (gc) {
     GI_GC_CASE(1)

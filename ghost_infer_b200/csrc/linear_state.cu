@@ -74,6 +74,7 @@ struct LsArgs {
   const void *q, *k, *v, *a_in, *b_in;
   long ldq, ldk, ldv, lda, ldb;
   const float *decay_c, *dt_bias;
+  const float *g_direct, *u_direct;      // per token and head, ready made: the decay itself and what multiplies the written value
   float* state;
   long state_ld;
   int state_rows;
@@ -114,7 +115,7 @@ linear_state_kernel(const LsArgs a) {
   const size_t o_ld = (size_t)a.heads * V;
   const T* qp = (const T*)a.q; const T* kp = (const T*)a.k; const T* vp = (const T*)a.v;
   const T* ap = (const T*)a.a_in; const T* bp = (const T*)a.b_in;
-  const float dc = a.decay_c[h];
+  const float dc = a.decay_c != nullptr ? a.decay_c[h] : 1.0f;
   const float rate = ap != nullptr ? expf(dc) : 0.f, bias = (ap != nullptr && a.dt_bias != nullptr) ? a.dt_bias[h] : 0.f;
 
   // a chunk's tokens made ready in buffer `buf` by the 128 preparing threads together.  First every thread loads its share
@@ -208,6 +209,8 @@ linear_state_kernel(const LsArgs a) {
     if (pt < n) {
       sg[pt] = ap != nullptr ? expf(-rate * ls_softplus(av + bias)) : dc;
       sb[pt] = bp != nullptr ? 1.0f / (1.0f + expf(-bv)) : 1.0f;
+      if (a.g_direct != nullptr) sg[pt] = a.g_direct[(tokc + pt) * a.heads + h];
+      if (a.u_direct != nullptr) sb[pt] = a.u_direct[(tokc + pt) * a.heads + h];
     }
     if (a.unit_norm) {
       ls_prep_barrier();             // the chunk's rows are in shared memory
@@ -305,6 +308,8 @@ linear_state_kernel(const LsArgs a) {
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
         u = sb[t] * (u - g * d);
+      } else if (a.u_direct != nullptr) {
+        u *= sb[t];
       }
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -393,17 +398,29 @@ extern "C" int gi_linear_state(float* o, const void* q, long ldq, const void* k,
                                const float* dt_bias, float* state, long state_ld, int state_rows, const int* cu_seqlens,
                                const int* seq_slots, int n_seqs, int heads, int qk_heads, int K, int V, int in_act,
                                int unit_norm, float norm_eps, float q_scale, int delta, int n_tokens, void* stream) {
+  return gi_linear_state_gated(o, q, ldq, k, ldk, v, ldv, a_in, lda, b_in, ldb, dtype, decay_c, dt_bias, nullptr, nullptr, state,
+                               state_ld, state_rows, cu_seqlens, seq_slots, n_seqs, heads, qk_heads, K, V, in_act, unit_norm,
+                               norm_eps, q_scale, delta, n_tokens, stream);
+}
+
+extern "C" int gi_linear_state_gated(float* o, const void* q, long ldq, const void* k, long ldk, const void* v, long ldv,
+                                     const void* a_in, long lda, const void* b_in, long ldb, int dtype, const float* decay_c,
+                                     const float* dt_bias, const float* g_direct, const float* u_direct, float* state,
+                                     long state_ld, int state_rows, const int* cu_seqlens, const int* seq_slots, int n_seqs,
+                                     int heads, int qk_heads, int K, int V, int in_act, int unit_norm, float norm_eps,
+                                     float q_scale, int delta, int n_tokens, void* stream) {
   if (n_seqs <= 0) return GI_OK;
   if (heads <= 0 || qk_heads <= 0 || heads % qk_heads || K <= 0 || V <= 0)
     return gi::fail(GI_ERR_ARG, "linear_state: bad sizes (heads %d, query/key heads %d, keys %d, values %d)", heads, qk_heads, K, V);
   if (K > 32 * LS_LANES) return gi::fail(GI_ERR_UNSUPPORTED, "linear_state: keys of %d numbers (at most %d)", K, 32 * LS_LANES);
-  if (!o || !q || !k || !v || !decay_c || !state || !cu_seqlens || !seq_slots) return gi::fail(GI_ERR_ARG, "linear_state: a missing pointer");
+  if (!o || !q || !k || !v || (!decay_c && !g_direct) || !state || !cu_seqlens || !seq_slots) return gi::fail(GI_ERR_ARG, "linear_state: a missing pointer");
+  if (u_direct != nullptr && delta) return gi::fail(GI_ERR_ARG, "linear_state: ready-made write strengths do not go with the delta rule");
   if (delta && b_in == nullptr) return gi::fail(GI_ERR_ARG, "linear_state: the delta rule needs its write strengths");
   if (state_ld < (long)heads * K * V) return gi::fail(GI_ERR_ARG, "linear_state: state rows of %ld floats, wanted %ld", state_ld, (long)heads * K * V);
   LsArgs a;
   a.o = o; a.q = q; a.k = k; a.v = v; a.a_in = a_in; a.b_in = b_in;
   a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.lda = lda; a.ldb = ldb;
-  a.decay_c = decay_c; a.dt_bias = dt_bias; a.state = state; a.state_ld = state_ld; a.state_rows = state_rows;
+  a.decay_c = decay_c; a.dt_bias = dt_bias; a.g_direct = g_direct; a.u_direct = u_direct; a.state = state; a.state_ld = state_ld; a.state_rows = state_rows;
   a.cu_seqlens = cu_seqlens; a.seq_slots = seq_slots;
   a.heads = heads; a.qk_heads = qk_heads; a.K = K; a.V = V; a.in_act = in_act; a.unit_norm = unit_norm;
   // sixteen bytes of a column at a time where every column of every slot starts on such a boundary

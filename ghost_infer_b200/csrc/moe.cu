@@ -49,10 +49,11 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sgate, const T* __restrict__ h, long ldh,
              const TW* __restrict__ w_router, const TW* __restrict__ w_sg, int n_tokens, int width, int experts, int top,
-             int vec, int score_mode) {
+             int vec, int score_mode, const float* __restrict__ correction, float weight_scale) {
   extern __shared__ __align__(16) float sm[];
   float* hs = sm;                          // [width] (rounded up to a multiple of 8)
   float* lg = sm + ((width + 7) / 8) * 8;  // [experts]
+  float* ps = lg + experts;                // [experts] (score_mode 2: every expert's share of the softmax over all of them)
   gi::pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -82,6 +83,25 @@ route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__
   }
   __syncthreads();
   if (warp != 0) return;
+  if (score_mode == 2) {
+    // the softmax over all experts; the choice is made by share + correction, the weights use the shares themselves
+    float top_z = -INFINITY;
+    for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, lg[e]);
+    top_z = gi::warp_max(top_z);
+    float den = 0.f;
+    for (int e = lane; e < experts; e += 32) {
+      const float p = expf(lg[e] - top_z);
+      ps[e] = p;
+      den += p;
+    }
+    den = gi::warp_sum(den);
+    for (int e = lane; e < experts; e += 32) {
+      const float p = ps[e] / den;
+      ps[e] = p;
+      lg[e] = p + (correction != nullptr ? correction[e] : 0.f);
+    }
+    __syncwarp();
+  }
   float first = 0.f, sum = 0.f, mine = 0.f;      // lane k keeps the k-th chosen logit (top <= 32)
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -99,7 +119,8 @@ route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__
     if (at == 0x7fffffff) at = k < experts ? k : 0;      // every logit a NaN: any expert, never an index outside
     if (k == 0) first = best;
     // score_mode 0: the weights are the softmax over the chosen logits; 1: each chosen logit's own sigmoid, as it is
-    const float ex = score_mode == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
+    const float ex = score_mode == 2 ? ps[at < experts ? at : 0]
+                                     : (score_mode == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first));
     sum += ex;
     if (lane == k) mine = ex;
     if (lane == 0) {
@@ -108,7 +129,8 @@ route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__
     }
     __syncwarp();
   }
-  if (lane < top) wts[(size_t)t * top + lane] = score_mode == 1 ? mine : mine / sum;
+  if (lane < top)
+    wts[(size_t)t * top + lane] = score_mode == 2 ? mine / (sum + 1e-20f) * weight_scale : (score_mode == 1 ? mine : mine / sum);
 }
 
 // ---- plan ------------------------------------------------------------------------------------------------------
@@ -189,13 +211,24 @@ __device__ __forceinline__ bool tile_rows(const int* __restrict__ offsets, int e
   return false;
 }
 
+// What a gated expert keeps of its two sums.  limit <= 0: silu(g) * u.  limit > 0: the clamped form g' = min(g, limit),
+// u' = clamp(u, -limit, limit), g' * sigmoid(alpha g') * (u' + 1).
+__device__ __forceinline__ float gated_value(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 // DUAL: two accumulators (gate rows n, up rows f + n of the expert's matrix), out = silu(gate) * up in the rows' type.
 // else: out (float) = a W^T.
 template <typename TA, typename TW, bool DUAL>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, const TW* __restrict__ W, long w_stride,
                    const int* __restrict__ offsets, const int* __restrict__ perm, int top, int experts, int N, int K,
-                   int interleaved, int act_out) {
+                   int interleaved, int act_out, float limit, float alpha) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[DUAL ? BK : 1][BN + 4];
@@ -267,8 +300,7 @@ expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, 
       const int n = n0 + tx * TN + j;
       if (n >= N) continue;
       if (DUAL) {
-        const float g = acc[i][j];
-        gi::stf((TA*)out_ + (size_t)r * N + n, g / (1.0f + expf(-g)) * acu[i][j]);
+        gi::stf((TA*)out_ + (size_t)r * N + n, gated_value(acc[i][j], acu[i][j], limit, alpha));
       } else if (act_out) {          // a plain (ungated) hidden layer: relu squared, in the rows' type
         const float z = fmaxf(acc[i][j], 0.f);
         gi::stf((TA*)out_ + (size_t)r * N + n, z * z);
@@ -297,7 +329,7 @@ template <typename T, bool DUAL>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, const T* __restrict__ W, long w_stride,
                    const int* __restrict__ offsets, const int* __restrict__ perm, int top, int N, int K, int interleaved,
-                   int act_out) {
+                   int act_out, float limit, float alpha) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* As = reinterpret_cast<T*>(smem_raw);            // [GEMV_ROWS][K]
   constexpr int VN = Vec16<T>::N;
@@ -367,7 +399,7 @@ expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, c
           const float g = gi::warp_sum(acc[jj][r]);
           if (DUAL) {
             const float u = gi::warp_sum(acu[jj][r]);
-            if (lane == 0 && n < N) gi::stf((T*)out_ + (size_t)(r0 + r) * N + n, g / (1.0f + expf(-g)) * u);
+            if (lane == 0 && n < N) gi::stf((T*)out_ + (size_t)(r0 + r) * N + n, gated_value(g, u, limit, alpha));
           } else if (lane == 0 && n < N) {
             if (act_out) {
               const float z = fmaxf(g, 0.f);
@@ -424,12 +456,19 @@ extern "C" int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, i
 extern "C" int gi_moe_route_scored(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
                                    const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, int score_mode,
                                    void* stream) {
+  return gi_moe_route_shares(ids, wts, sgate, h, dtype, ldh, w_router, w_sg, w_dtype, n_tokens, width, experts, top, score_mode,
+                             nullptr, 1.0f, stream);
+}
+
+extern "C" int gi_moe_route_shares(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
+                                   const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, int score_mode,
+                                   const float* correction, float weight_scale, void* stream) {
   if (n_tokens <= 0) return GI_OK;
-  if (score_mode != 0 && score_mode != 1) return gi::fail(GI_ERR_ARG, "router: unknown kind of weights %d", score_mode);
+  if (score_mode < 0 || score_mode > 2) return gi::fail(GI_ERR_ARG, "router: unknown kind of weights %d", score_mode);
   if (experts < 1 || top < 1 || top > experts || top > 32 || experts > 8192)
     return gi::fail(GI_ERR_UNSUPPORTED, "router: %d of %d experts (at most 32 of 8192)", top, experts);
   if (w_sg != nullptr && sgate == nullptr) return gi::fail(GI_ERR_ARG, "router: a shared gate needs somewhere to go");
-  const size_t smem = (((size_t)width + 7) / 8 * 8 + (size_t)experts) * sizeof(float);
+  const size_t smem = (((size_t)width + 7) / 8 * 8 + 2 * (size_t)experts) * sizeof(float);
   if (smem > 200 * 1024) return gi::fail(GI_ERR_UNSUPPORTED, "router: rows of %d values are wider than its shared memory", width);
   const int per = w_dtype == GI_F32 ? 4 : 8;
   const int vec = (width % per == 0 && !(((uintptr_t)w_router | (uintptr_t)w_sg) & 15)) ? 1 : 0;
@@ -439,7 +478,7 @@ extern "C" int gi_moe_route_scored(int* ids, float* wts, float* sgate, const voi
       if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e == cudaSuccess)
         e = gi::launch(kern, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, ids, wts, sgate, (const T*)h, ldh,
-                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top, vec, score_mode);
+                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top, vec, score_mode, correction, weight_scale);
   }));
   return gi::check(e, "router");
 }
@@ -466,6 +505,13 @@ extern "C" int gi_moe_plan(int* offsets, int* perm, int* inv, int* scratch, cons
 extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
                                    const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
                                    int interleaved, void* stream) {
+  return gi_moe_gemm_gate_up_clamped(out, dtype, a, lda, w, w_dtype, w_stride, offsets, perm, entries, top, experts, f, k, interleaved,
+                                     0.f, 1.0f, stream);
+}
+
+extern "C" int gi_moe_gemm_gate_up_clamped(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
+                                           const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
+                                           int interleaved, float limit, float alpha, void* stream) {
   if (entries <= 0) return GI_OK;
   if (f <= 0 || k <= 0 || top < 1) return gi::fail(GI_ERR_ARG, "expert product: bad sizes");
   if (interleaved && f % 8 != 0) return gi::fail(GI_ERR_ARG, "expert product: interleaved rows need a width that is a multiple of 8");
@@ -478,7 +524,7 @@ extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
           e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, out, (const T*)a, lda, (const T*)w, w_stride,
-                         offsets, perm, top, f, k, interleaved, 0);
+                         offsets, perm, top, f, k, interleaved, 0, limit, alpha);
     });
     return gi::check(e, "expert product (gate, up; few rows)");
   }
@@ -488,7 +534,7 @@ extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, true>, grid, dim3(256), 0, (cudaStream_t)stream, out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k, interleaved, 0)));
+                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k, interleaved, 0, limit, alpha)));
   return gi::check(e, "expert product (gate, up)");
 }
 
@@ -511,7 +557,7 @@ extern "C" int gi_moe_gemm_rows(void* out, const void* a, int dtype, long lda, c
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
           e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, (void*)out, (const T*)a, lda, (const T*)w,
-                         w_stride, offsets, (const int*)nullptr, 1, n, k, 0, act_out);
+                         w_stride, offsets, (const int*)nullptr, 1, n, k, 0, act_out, 0.f, 1.0f);
     });
     return gi::check(e, "expert product (down; few rows)");
   }
@@ -521,7 +567,7 @@ extern "C" int gi_moe_gemm_rows(void* out, const void* a, int dtype, long lda, c
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, false>, grid, dim3(256), 0, (cudaStream_t)stream, (void*)out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k, 0, act_out)));
+                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k, 0, act_out, 0.f, 1.0f)));
   return gi::check(e, "expert product (down)");
 }
 

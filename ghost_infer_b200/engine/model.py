@@ -115,11 +115,13 @@ class Model:
     def memory_requests(self):
         out = []
         for i, e in enumerate(self.spec.schedule):
-            mixer = self.layers[e.layer].block.mixer
-            if mixer is None:                                  # a layer without a mixer keeps nothing per sequence
-                out.append((i, None, None, e.memory_of))
+            block = self.layers[e.layer].block
+            mixer = block.mixer
+            own = block.state_request()                        # what the arrangement itself keeps per sequence (never borrowed)
+            if mixer is None:                                  # a layer without a mixer keeps nothing else per sequence
+                out.append((i, None, None, e.memory_of, own))
             else:
-                out.append((i, mixer.cache_request(), mixer.state_request(), e.memory_of))
+                out.append((i, mixer.cache_request(), mixer.state_request(), e.memory_of, own))
         return out
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None,

@@ -222,12 +222,18 @@ class Engine:
         x = model.embedding.forward(ctx.tokens)
         if getattr(model, "embedding_norm", None) is not None:      # the stream stays 32-bit
             x = model.embedding_norm.forward(x, out_dtype=torch.float32)
+        streams = int(getattr(model.spec, "streams", 0) or 0)
+        if streams:                                                  # several copies of the stream, equal at the start
+            x = ops.stream_expand(x, streams)
         x = ops.as_carrier(x)
         for i, e in enumerate(model.spec.schedule):
             model.layers[e.layer].block.forward(x, ctx, self.cache.memory(i))
         if ctx.logit_rows is None:
             ops.drop_pending(x)
             return None
+        if streams:                                                  # the copies' sum, on the wanted rows only
+            ops.settle(x)
+            return model.head.forward(model.final_norm.forward(ops.stream_sum(x, streams, ctx.logit_rows)))
         if not getattr(model.final_norm, "settles_pending", False):
             ops.settle(x)
         h = model.final_norm.forward(x, rows=ctx.logit_rows)

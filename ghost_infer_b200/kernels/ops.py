@@ -113,6 +113,22 @@ def _bind():
         "gi_side_gate": [P, P, L, I, P, L, I, P, I, I, I, P],
         "gi_act_rows": [P, P, L, I, I, I, P],
         "gi_linear_state": [P, P, L, P, L, P, L, P, L, P, L, I, P, P, P, L, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
+        "gi_linear_state_gated": [P, P, L, P, L, P, L, P, L, P, L, I, P, P, P, P, P, L, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
+        "gi_mlstm_gates": [P, P, P, P, L, P, L, P, P, L, I, P, P, F, F, P, L, I, P, P, I, I, I, P],
+        "gi_stream_expand": [P, P, I, I, I, P],
+        "gi_stream_sum": [P, P, P, I, I, I, P],
+        "gi_hyper_read": [P, I, P, P, P, I, P, I, I, I, F, P],
+        "gi_input_conv": [P, P, I, P, I, P, L, I, P, I, I, I, P],
+        "gi_hyper_write": [P, P, P, P, I, I, P, P, P, P, L, I, P, I, I, I, I, P],
+        "gi_scale_rows": [P, F, L, P],
+        "gi_head_prepare": [P, L, I, P, L, P, P, P, P, P, I, I, I, I, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, P],
+        "gi_head_gate": [P, P, I, P, L, I, I, I, P],
+        "gi_scaled_norm_gate": [P, I, P, P, P, L, P, I, I, I, I, F, P],
+        "gi_clamped_glu": [P, P, L, I, I, I, F, F, P],
+        "gi_moe_route_shares": [P, P, P, P, I, L, P, P, I, I, I, I, I, I, P, F, P],
+        "gi_moe_gemm_gate_up_clamped": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, I, F, F, P],
+        "gi_attn_prefill_generic_ex3": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, L, I, P],
+        "gi_attn_decode_generic_ex3": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, L, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -844,21 +860,22 @@ def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Te
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                          window: Optional[int], out: torch.Tensor, *, v_dim: Optional[int] = None, softcap: float = 0.0,
-                         sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+                         sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
     """`v_dim`: width of a value head when it is not the keys' (`vcache` is then [pages, kv heads, 64, v_dim]);
     `softcap` > 0: scores become cap * tanh(score / cap); `sinks` float32 [heads]: a term exp(sink) in each head's
-    softmax denominator without key or value; `chunk`: a query sees keys of its own chunk floor(pos / chunk) only."""
+    softmax denominator without key or value; `chunk`: a query sees keys of its own chunk floor(pos / chunk) only;
+    `keep_first`: with a window, the sequence's first so many positions stay visible as well."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
     if kcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("queries, cache and attention output must share a dtype")
-    _check(lib, lib.gi_attn_prefill_generic_ex(
+    _check(lib, lib.gi_attn_prefill_generic_ex3(
         out.data_ptr(), ldo, q.data_ptr(), ldq, _dt(q, "queries"), kcache.data_ptr(), vcache.data_ptr(),
         _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
         _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
         float(scale), int(window or 0), int(v_dim or head_dim), float(softcap or 0.0), _sinks_ptr(sinks, n_heads),
-        int(chunk or 0), _stream()))
+        int(chunk or 0), int(v_dim or head_dim), int(keep_first or 0), _stream()))
     return out
 
 
@@ -867,8 +884,8 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
                         head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
                         part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                         own_tiles: int = 0, *, v_dim: Optional[int] = None, softcap: float = 0.0,
-                        sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
-    """`v_dim`, `softcap`, `sinks`, `chunk`: as `attn_prefill_generic`'s.
+                        sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
+    """`v_dim`, `softcap`, `sinks`, `chunk`, `keep_first`: as `attn_prefill_generic`'s.
     `own_tiles` > 0: slice s of a sequence is tiles [s * own_tiles, (s + 1) * own_tiles) of its own span (32 keys a
     tile), whatever `n_splits` is, which must then cover the longest sequence; 0: every span is cut into `n_splits`
     equal slices."""
@@ -884,13 +901,13 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
             raise KernelError("attention scratch for outputs is too small")
         if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
             raise KernelError("attention scratch for maxima and sums is too small")
-    _check(lib, lib.gi_attn_decode_generic_ex(
+    _check(lib, lib.gi_attn_decode_generic_ex3(
         out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
         part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, _dt(q, "queries"),
         kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"), block_table.shape[1],
         _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"), n_seqs, n_heads, n_kv, head_dim, float(scale),
         int(window or 0), int(n_splits), int(own_tiles), int(v_dim or head_dim), float(softcap or 0.0),
-        _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()), 2 if n_splits > 1 else 1)
+        _sinks_ptr(sinks, n_heads), int(chunk or 0), int(v_dim or head_dim), int(keep_first or 0), _stream()), 2 if n_splits > 1 else 1)
     return out
 
 
@@ -1286,16 +1303,20 @@ def kv_store(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, me
 
 def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, v_dim: int, scale: float,
                       out: torch.Tensor, *, window: Optional[int] = None, chunk: Optional[int] = None, softcap: float = 0.0,
-                      sinks: Optional[torch.Tensor] = None, plan=None) -> torch.Tensor:
+                      sinks: Optional[torch.Tensor] = None, plan=None, keep_first: int = 0) -> torch.Tensor:
     """Attention of a step's tokens over the cache with any of: values of another width than the keys, capped scores,
-    a sink per head, chunks of positions, a window.  The cache already holds the step's own keys and values."""
+    a sink per head, chunks of positions, a window (which may keep the first `keep_first` positions visible as well).
+    The cache already holds the step's own keys and values."""
     if memory.k is None:
         raise KernelError("attention needs a cache to read from")
+    keep_first = int(keep_first or 0) if window else 0
     opts = dict(v_dim=v_dim, softcap=softcap, sinks=sinks, chunk=chunk)
+    if keep_first:
+        opts["keep_first"] = keep_first
     if step.is_decode:
         if plan is None:
             plan = attn_general_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, n_kv, window, chunk, qkv.dtype,
-                                            head_dim, v_dim)
+                                            head_dim, v_dim, keep_first=keep_first)
         kind, n_splits, own_tiles = plan
         part_o = part_ml = None
         if n_splits > 1:
@@ -1317,6 +1338,10 @@ def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, 
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
                                    n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
                                    **opts)
+    if keep_first:
+        # TENSOR-CORE-KEPT-FIRST
+        return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
+                                    step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, **opts)
     if (TUNE["attn_general_tc"] and TUNE["attn_prefill_tcgen05"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16
             and head_dim == v_dim and head_dim in (64, 128) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
             and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
@@ -1364,14 +1389,15 @@ def attn_general_tc_ok(dtype: torch.dtype, head_dim: int, v_dim: int) -> bool:
 
 def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, window: Optional[int],
                              chunk: Optional[int], dtype: torch.dtype, head_dim: Optional[int] = None,
-                             v_dim: Optional[int] = None, kv_lens=None):
+                             v_dim: Optional[int] = None, kv_lens=None, keep_first: int = 0):
     """(kernel, slices in the launch, tiles per slice) for one-token steps of `attention_general`.
     "tensor cores" (bfloat16, sizes the kernel takes): the cut `attn_decode_plan` makes for the keys-on-rows kernel, over
     the span a token can see.  "plain": slices of eight 32-key tiles counted from the start of that span (the last
     `window` positions, the token's chunk, or everything), so that a sequence's sums are formed in the same order
     whatever else the step holds."""
     limit = window or chunk
-    if head_dim is not None and attn_general_tc_ok(dtype, head_dim, v_dim or head_dim):
+    keep_first = int(keep_first or 0) if window else 0
+    if head_dim is not None and attn_general_tc_ok(dtype, head_dim, v_dim or head_dim) and not keep_first:
         seen = min(max_kv_len, int(limit) + 15) if limit else max_kv_len
         lens = [min(int(n), seen) for n in kv_lens] if kv_lens else None
         n_splits, own = attn_decode_plan(n_seqs, seen, sm_count, n_heads, n_kv, 64 if max(head_dim, v_dim or head_dim) <= 64 else 128,
@@ -1381,7 +1407,7 @@ def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_head
     for limit in (window, chunk):
         if limit:
             span = min(span, int(limit) + 31)
-    tiles = (span + 31) // 32 + (1 if (window or chunk) else 0)
+    tiles = (span + 31) // 32 + (1 if (window or chunk) else 0) + (keep_first + 31) // 32
     return "plain", max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
 
 
@@ -1551,8 +1577,9 @@ def moe_rows_product(rows: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
 
 
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor,
-                top: int, interleaved: bool = False) -> torch.Tensor:
-    """Every chosen expert's output, float32 [entries (in sorted order), width]: down_e(silu(gate_e h) * (up_e h)).
+                top: int, interleaved: bool = False, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+    """Every chosen expert's output, float32 [entries (in sorted order), width]: down_e(silu(gate_e h) * (up_e h)), or with
+    `limit` > 0 the clamped form down_e(g sigmoid(alpha g) (u + 1)), g = min(gate_e h, limit), u = clamp(up_e h, +-limit).
     `w_gate_up` [experts, 2 f, width] (gate rows, then up rows; or, `interleaved`, blocks [8 gate | 8 up]), `w_down`
     [experts, width, f].  Few entries (one-token steps) take kernels that stream the chosen experts' matrices once."""
     lib = _bind()
@@ -1566,10 +1593,10 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         raise KernelError("expert weights must share a type")
     entries = perm.numel()
     inter = torch.empty((entries, f), dtype=h.dtype, device=h.device)
-    _check(lib, lib.gi_moe_gemm_gate_up(inter.data_ptr(), _dt(h, "activations"), h.data_ptr(), lda, w_gate_up.data_ptr(),
-                                        _dt(w_gate_up, "expert weights"), w_gate_up.stride(0), _i32(offsets, "offsets"),
-                                        _i32(perm, "permutation"), entries, int(top), experts, f, width, int(interleaved),
-                                        _stream()))
+    _check(lib, lib.gi_moe_gemm_gate_up_clamped(inter.data_ptr(), _dt(h, "activations"), h.data_ptr(), lda, w_gate_up.data_ptr(),
+                                                _dt(w_gate_up, "expert weights"), w_gate_up.stride(0), _i32(offsets, "offsets"),
+                                                _i32(perm, "permutation"), entries, int(top), experts, f, width, int(interleaved),
+                                                float(limit), float(alpha), _stream()))
     down = torch.empty((entries, width), dtype=torch.float32, device=h.device)
     _check(lib, lib.gi_moe_gemm_down(down.data_ptr(), inter.data_ptr(), _dt(inter, "activations"), f, w_down.data_ptr(),
                                      _dt(w_down, "expert weights"), w_down.stride(0), _i32(offsets, "offsets"), entries,
@@ -2062,3 +2089,260 @@ def linear_state(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch
         state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads, qk_heads, key_dim,
         v_dim, int(in_act), int(unit_norm), float(norm_eps), float(q_scale), int(delta), int(n), _stream()))
     return o
+
+
+def linear_state_gated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, step, heads: int, key_dim: int,
+                       v_dim: int, decay: torch.Tensor, write: torch.Tensor) -> torch.Tensor:
+    """The recurrence S <- decay_t S + k_t (write_t v_t)^T; o_t = S^T q_t with both gates ready made, float32 [tokens, heads],
+    from and into `state` ([slots + 1, >= heads * key_dim * v_dim] float32).  Returns float32 [tokens, heads * v_dim]."""
+    lib = _bind()
+    n = q.shape[0]
+    for t, what, width in ((q, "queries", heads * key_dim), (k, "keys", heads * key_dim), (v, "values", heads * v_dim)):
+        _cuda(t, what)
+        if t.dtype != q.dtype or tuple(t.shape) != (n, width) or t.stride(1) != 1:
+            raise KernelError(f"{what} must be [{n}, {width}] rows of the queries' type, got {t.dtype} {tuple(t.shape)}")
+    for t, what in ((decay, "decays"), (write, "write strengths")):
+        if t.dtype != torch.float32 or tuple(t.shape) != (n, heads) or not t.is_contiguous() or not t.is_cuda:
+            raise KernelError(f"{what} must be contiguous float32 [{n}, {heads}] on the device")
+    if state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < heads * key_dim * v_dim:
+        raise KernelError("the recurrence needs its per-sequence state as a contiguous float32 matrix of at least heads x keys x values")
+    o = torch.empty((n, heads * v_dim), dtype=torch.float32, device=q.device)
+    _check(lib, lib.gi_linear_state_gated(
+        o.data_ptr(), q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), None, 0, None, 0,
+        _dt(q, "queries"), None, None, decay.data_ptr(), write.data_ptr(), state.data_ptr(), state.stride(0), state.shape[0],
+        _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads, heads, key_dim, v_dim, 0, 0,
+        1e-6, 1.0, 0, int(n), _stream()))
+    return o
+
+
+def mlstm_gates(q: torch.Tensor, k: torch.Tensor, gate_i: torch.Tensor, gate_f: torch.Tensor, bias_i: Optional[torch.Tensor],
+                bias_f: Optional[torch.Tensor], cap: float, q_scale: float, state: torch.Tensor, state_offset: int, step, heads: int,
+                key_dim: int):
+    """(keep, put, out_scale), each float32 [tokens, heads], of a matrix memory with a running maximum; the normalizer n and
+    the maximum m live in `state` ([slots + 1, ...] float32) from `state_offset` on, heads * (key_dim + 1) floats."""
+    lib = _bind()
+    n = q.shape[0]
+    for t, what, width in ((q, "queries", heads * key_dim), (k, "keys", heads * key_dim), (gate_i, "input gates", heads),
+                           (gate_f, "forget gates", heads)):
+        _cuda(t, what)
+        if t.dtype != q.dtype or tuple(t.shape) != (n, width) or t.stride(1) != 1:
+            raise KernelError(f"{what} must be [{n}, {width}] rows of the queries' type, got {t.dtype} {tuple(t.shape)}")
+    if gate_i.stride(0) != gate_f.stride(0):
+        raise KernelError("the two gates' rows must be equally far apart")
+    for t in (bias_i, bias_f):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous() or not t.is_cuda):
+            raise KernelError(f"a gate's bias must be {heads} float32 values on the device")
+    if (state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous()
+            or state.shape[1] < state_offset + heads * (key_dim + 1)):
+        raise KernelError("the gates need heads x (keys + 1) float32 numbers of per-sequence state")
+    keep, put, scale = (torch.empty((n, heads), dtype=torch.float32, device=q.device) for _ in range(3))
+    _check(lib, lib.gi_mlstm_gates(
+        keep.data_ptr(), put.data_ptr(), scale.data_ptr(), q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), gate_i.data_ptr(),
+        gate_f.data_ptr(), gate_i.stride(0), _dt(q, "queries"), bias_i.data_ptr() if bias_i is not None else None,
+        bias_f.data_ptr() if bias_f is not None else None, float(cap), float(q_scale), state.data_ptr() + 4 * int(state_offset),
+        state.stride(0), state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads,
+        key_dim, _stream()))
+    return keep, put, scale
+
+
+# ---- several copies of the residual stream ------------------------------------------------------------------------------
+def stream_expand(e: torch.Tensor, streams: int) -> torch.Tensor:
+    """float32 [tokens, streams * d]: every copy of the stream starts as the row of `e` (float32 [tokens, d])."""
+    lib = _bind()
+    _cuda(e, "embedded tokens")
+    if e.dtype != torch.float32 or e.dim() != 2 or not e.is_contiguous():
+        raise KernelError("the embedded tokens must be contiguous float32 rows")
+    n, d = e.shape
+    x = torch.empty((n, streams * d), dtype=torch.float32, device=e.device)
+    _check(lib, lib.gi_stream_expand(x.data_ptr(), e.data_ptr(), n, int(streams), d, _stream()))
+    return x
+
+
+def stream_sum(x: torch.Tensor, streams: int, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [rows, d]: the sum of the copies of the chosen tokens (all tokens without `rows`)."""
+    lib = _bind()
+    _cuda(x, "residual streams")
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or x.shape[1] % streams:
+        raise KernelError("the residual streams must be contiguous float32 rows of streams x width numbers")
+    d = x.shape[1] // streams
+    n = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((n, d), dtype=torch.float32, device=x.device)
+    _check(lib, lib.gi_stream_sum(out.data_ptr(), x.data_ptr(), _i32(rows, "row selection"), n, int(streams), d, _stream()))
+    return out
+
+
+def hyper_read(x: torch.Tensor, blend: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h = rmsnorm(sum_s blend[s] x[:, s]) * weight in `out_dtype`; `zero` (float32 [tokens, d]) is set to zero in the same pass."""
+    lib = _bind()
+    _cuda(x, "residual streams")
+    streams = blend.numel()
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or x.shape[1] % streams:
+        raise KernelError("the residual streams must be contiguous float32 rows of streams x width numbers")
+    n, d = x.shape[0], x.shape[1] // streams
+    if blend.dtype != torch.float32 or not blend.is_contiguous() or not blend.is_cuda or weight.numel() != d or not weight.is_contiguous():
+        raise KernelError("hyper_read: the blend must be float32 [streams], the weight [width]")
+    if zero is not None and (zero.dtype != torch.float32 or tuple(zero.shape) != (n, d) or not zero.is_contiguous()):
+        raise KernelError("hyper_read: the rows to zero must be contiguous float32 [tokens, width]")
+    h = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    _check(lib, lib.gi_hyper_read(h.data_ptr(), _DT[out_dtype], x.data_ptr(), blend.data_ptr(), weight.data_ptr(), _dt(weight, "norm weight"),
+                                  zero.data_ptr() if zero is not None else None, n, streams, d, float(eps), _stream()))
+    return h
+
+
+def _conv_state(state: Optional[torch.Tensor], taps: int, d: int):
+    if taps <= 1:
+        return None, 0, 0
+    if state is None or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < (taps - 1) * d:
+        raise KernelError("the input convolution needs (taps - 1) x width float32 numbers of per-sequence state")
+    return state.data_ptr(), state.stride(0), state.shape[0]
+
+
+def input_conv(h: torch.Tensor, taps_w: torch.Tensor, state: Optional[torch.Tensor], step) -> torch.Tensor:
+    """h + conv(h): a causal convolution per channel over the tokens of each sequence (`taps_w` [width, taps], the last tap the
+    token's own), inputs older than the step from `state` ([slots + 1, (taps - 1) * width] float32, oldest first)."""
+    lib = _bind()
+    _cuda(h, "inputs")
+    n, d = h.shape
+    taps = taps_w.shape[1]
+    if not h.is_contiguous() or tuple(taps_w.shape) != (d, taps) or not taps_w.is_contiguous():
+        raise KernelError("input_conv: contiguous rows and taps [width, taps] are wanted")
+    sp, sld, srows = _conv_state(state, taps, d)
+    out = torch.empty_like(h)
+    _check(lib, lib.gi_input_conv(out.data_ptr(), h.data_ptr(), _dt(h, "inputs"), taps_w.data_ptr(), _dt(taps_w, "taps"), sp, sld, srows,
+                                  _i32(step.token_slots, "slots"), n, d, taps, _stream()))
+    return out
+
+
+def hyper_write(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, share: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                gate_bias: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None,
+                taps: int = 1, step=None) -> None:
+    """x[:, to] = sum_s mix[s, to] x[:, s] + share[to] * y * sigmoid(gate + gate_bias), all copies at once; with `state`, the
+    last `taps` - 1 rows of `h` of every sequence become its convolution state."""
+    lib = _bind()
+    _cuda(x, "residual streams")
+    streams = share.numel()
+    n, d = y.shape
+    if (x.dtype != torch.float32 or not x.is_contiguous() or tuple(x.shape) != (n, streams * d) or y.dtype != torch.float32
+            or not y.is_contiguous() or tuple(mix.shape) != (streams, streams) or mix.dtype != torch.float32 or share.dtype != torch.float32
+            or not mix.is_contiguous() or not share.is_contiguous()):
+        raise KernelError("hyper_write: float32 streams [tokens, streams x width], rows [tokens, width], mix [streams, streams]")
+    ref = gate if gate is not None else h
+    if gate is not None and (tuple(gate.shape) != (n, d) or not gate.is_contiguous()):
+        raise KernelError("hyper_write: the gate's rows must be contiguous [tokens, width]")
+    if h is not None and (tuple(h.shape) != (n, d) or not h.is_contiguous() or (gate is not None and h.dtype != gate.dtype)):
+        raise KernelError("hyper_write: the sublayer's inputs must be contiguous [tokens, width] rows of the gate's type")
+    sp, sld, srows = _conv_state(state, taps, d) if h is not None else (None, 0, 0)
+    _check(lib, lib.gi_hyper_write(
+        x.data_ptr(), y.data_ptr(), gate.data_ptr() if gate is not None else None, gate_bias.data_ptr() if gate_bias is not None else None,
+        _dt(ref, "rows") if ref is not None else F32, _dt(gate_bias, "gate bias") if gate_bias is not None else F32, mix.data_ptr(),
+        share.data_ptr(), h.data_ptr() if h is not None else None, sp, sld, srows, _i32(step.token_slots, "slots"), n, streams, d,
+        int(taps), _stream()))
+
+
+def scale_rows(x: torch.Tensor, c: float) -> torch.Tensor:
+    """x *= c in place (float32)."""
+    lib = _bind()
+    _cuda(x, "rows")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_rows: contiguous float32 rows are wanted")
+    _check(lib, lib.gi_scale_rows(x.data_ptr(), float(c), x.numel(), _stream()))
+    return x
+
+
+# ---- attention normed head by head, gated heads, clamped gated rows -----------------------------------------------------
+def head_prepare(rows: torch.Tensor, out_dtype: torch.dtype, biases, norm_weights, norms, eps: float, table: Optional[torch.Tensor],
+                 rot_dims: int, adjacent: bool, step, memory, n_heads: int, n_kv: int, head_dim: int, v_dim: int) -> torch.Tensor:
+    """The queries of float32 projection rows [q | k | v | ...], prepared head by head, in `out_dtype`; keys and values go to
+    the cache (`n_kv` 0: the rows hold queries only).  `biases` (q, k, v) and `norm_weights` (q, k) may hold None; `norms`
+    (q, k, v) says which parts are divided by each head's root mean square."""
+    lib = _bind()
+    _cuda(rows, "projection rows")
+    if rows.dtype != torch.float32 or rows.dim() != 2 or rows.stride(1) != 1:
+        raise KernelError("head_prepare: float32 projection rows are wanted")
+    n = rows.shape[0]
+    if rows.shape[1] < (n_heads + n_kv) * head_dim + n_kv * v_dim:
+        raise KernelError(f"projection rows of {rows.shape[1]} numbers cannot hold q, k and v")
+    if n_kv:
+        if memory.k is None or not memory.writes or memory.k.dtype != out_dtype or memory.v.dtype != out_dtype:
+            raise KernelError("head_prepare: keys and values need a cache of the step's type that this entry writes")
+        if (tuple(memory.k.shape[1:]) != (n_kv, 64, head_dim) or tuple(memory.v.shape[1:]) != (n_kv, 64, v_dim)
+                or not memory.k.is_contiguous() or not memory.v.is_contiguous()):
+            raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}] and [.., {v_dim}]")
+    given = [t for t in tuple(biases) + tuple(norm_weights) if t is not None]
+    w_dtype = given[0].dtype if given else torch.float32
+    if any(t.dtype != w_dtype or not t.is_contiguous() for t in given):
+        raise KernelError("head_prepare: biases and norm weights must share a type")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    q = torch.empty((n, n_heads * head_dim), dtype=out_dtype, device=rows.device)
+    bt = memory.block_table if n_kv else None
+    _check(lib, lib.gi_head_prepare(
+        q.data_ptr(), q.stride(0), _DT[out_dtype], rows.data_ptr(), rows.stride(0), ptr(biases[0]), ptr(biases[1]), ptr(biases[2]),
+        ptr(norm_weights[0]), ptr(norm_weights[1]), _DT[w_dtype], int(norms[0]), int(norms[1]), int(norms[2]), float(eps),
+        table.data_ptr() if (table is not None and rot_dims) else None, int(rot_dims) // 2, int(adjacent),
+        _i32(step.positions, "positions"), _i32(step.token_slots, "slots"), _i32(bt, "block table"), bt.shape[1] if bt is not None else 0,
+        memory.k.data_ptr() if n_kv else None, memory.v.data_ptr() if n_kv else None, n, n_heads, n_kv, head_dim, v_dim, _stream()))
+    return q
+
+
+def head_gate(a: torch.Tensor, gates: torch.Tensor, n_heads: int, v_dim: int) -> torch.Tensor:
+    """a[t, h, :] * sigmoid(gates[t, h]); `gates`: float32 rows with one number per head."""
+    lib = _bind()
+    _cuda(a, "attention output")
+    n = a.shape[0]
+    if not a.is_contiguous() or a.shape[1] != n_heads * v_dim or gates.dtype != torch.float32 or gates.stride(1) != 1 or gates.shape[1] < n_heads:
+        raise KernelError("head_gate: contiguous heads and float32 gate rows are wanted")
+    out = torch.empty_like(a)
+    _check(lib, lib.gi_head_gate(out.data_ptr(), a.data_ptr(), _dt(a, "attention output"), gates.data_ptr(), gates.stride(0), n, n_heads,
+                                 v_dim, _stream()))
+    return out
+
+
+def scaled_norm_gate(y: torch.Tensor, scale: Optional[torch.Tensor], gate: torch.Tensor, weight: torch.Tensor, n_heads: int,
+                     v_dim: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per head: v = y * scale[t, h]; v / sqrt(mean(v^2) + eps) * weight[h] * sigmoid(gate); y, gate float32 rows."""
+    lib = _bind()
+    _cuda(y, "read-outs")
+    n = y.shape[0]
+    if (y.dtype != torch.float32 or not y.is_contiguous() or y.shape[1] != n_heads * v_dim or gate.dtype != torch.float32
+            or gate.stride(1) != 1 or gate.shape[1] < n_heads * v_dim or weight.numel() != n_heads * v_dim or not weight.is_contiguous()):
+        raise KernelError("scaled_norm_gate: float32 read-outs and gate rows of heads x values numbers are wanted")
+    if scale is not None and (scale.dtype != torch.float32 or tuple(scale.shape) != (n, n_heads) or not scale.is_contiguous()):
+        raise KernelError("scaled_norm_gate: the scales must be contiguous float32 [tokens, heads]")
+    out = torch.empty((n, n_heads * v_dim), dtype=out_dtype, device=y.device)
+    _check(lib, lib.gi_scaled_norm_gate(out.data_ptr(), _DT[out_dtype], y.data_ptr(), scale.data_ptr() if scale is not None else None,
+                                        gate.data_ptr(), gate.stride(0), weight.data_ptr(), _dt(weight, "norm weight"), n, n_heads, v_dim,
+                                        float(eps), _stream()))
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """rows [gate | up] -> min(gate, limit) * sigmoid(alpha * that) * (clamp(up, -limit, limit) + 1), in the rows' type."""
+    lib = _bind()
+    _cuda(gate_up, "gate/up rows")
+    if gate_up.dim() != 2 or gate_up.stride(1) != 1 or gate_up.shape[1] % 2:
+        raise KernelError("gate/up rows must be a [rows, 2 * width] matrix")
+    n, f = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((n, f), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib, lib.gi_clamped_glu(out.data_ptr(), gate_up.data_ptr(), gate_up.stride(0), _dt(gate_up, "gate/up rows"), n, f, float(limit),
+                                   float(alpha), _stream()))
+    return out
+
+
+def moe_route_shares(h: torch.Tensor, w_router: torch.Tensor, top: int, correction: Optional[torch.Tensor], weight_scale: float):
+    """(ids int32 [tokens, top], weights float32 [tokens, top]): shares = softmax over all experts' logits; the `top` largest of
+    share + correction are chosen (the lower index on ties); weights = chosen shares / (their sum + 1e-20) * weight_scale."""
+    lib = _bind()
+    _cuda(h, "activations")
+    n, width = h.shape
+    experts = w_router.shape[0]
+    if w_router.dim() != 2 or w_router.shape[1] != width or not w_router.is_contiguous():
+        raise KernelError(f"router weights must be contiguous [experts, {width}]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts or not correction.is_contiguous()):
+        raise KernelError("the router's correction must be float32, one number per expert")
+    ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    _check(lib, lib.gi_moe_route_shares(ids.data_ptr(), wts.data_ptr(), None, h.data_ptr(), _dt(h, "activations"), _rows(h, "activations"),
+                                        w_router.data_ptr(), None, _dt(w_router, "router weights"), n, width, experts, int(top), 2,
+                                        correction.data_ptr() if correction is not None else None, float(weight_scale), _stream()))
+    return ids, wts

@@ -148,6 +148,10 @@ class Block:
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
         self.extra = dict(extra)
 
+    def state_request(self) -> Optional[StateRequest]:
+        """Fixed-size memory per sequence that the arrangement itself wants (`memory.block_state`); None: nothing."""
+        return None
+
     def parts(self):
         usual = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
         return usual + tuple(self.extra.values())

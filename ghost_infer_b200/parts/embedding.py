@@ -1,7 +1,7 @@
 """Token embedding and output head.
 
-x[t] = E[token_t] (src/model.rs:987-990), times `scale` where a model names one; logits = W normed with no bias, no cap, no
-scaling, where W is the embedding table when the model ties them (src/model.rs:637-638, :1183-1186).
+x[t] = E[token_t] (src/model.rs:987-990), times `scale` where a model names one; logits = W normed with no bias and no cap (times
+`scale` where a model names one), where W is the embedding table when the model ties them (src/model.rs:637-638, :1183-1186).
 """
 from __future__ import annotations
 
@@ -42,6 +42,7 @@ class LinearHead(Part):
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.tied = bool(params.get("tied", False))
+        self.scale = float(params.get("scale", 1.0))        # logits = scale * (W h)
         self.weight: Optional[torch.Tensor] = None
 
     def weights(self) -> List[WeightSpec]:
@@ -62,4 +63,5 @@ class LinearHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         with ops.bucket("logits"):
-            return linear(h, self.weight, out_dtype=torch.float32)
+            logits = linear(h, self.weight, out_dtype=torch.float32)
+            return logits if self.scale == 1.0 else ops.scale_rows(logits, self.scale)

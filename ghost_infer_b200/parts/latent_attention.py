@@ -9,7 +9,8 @@ of `v_dim` numbers, a latent of `rank` numbers and a query latent of `q_rank`:
     score_h(i, j) = (q_h,unrot(i) . k_h(j) + rot(q_h,rot(i)) . rot(kr(j))) * scale,   j <= i,   softmax,   out = W_o [sum p v_h]
 
 The position encoding (`params["position"]`, a rotary part) turns the rotated parts only; values are not rotated; `scale`
-is used as given.  Only c and the rotated kr are cached: one row [c | kr] per position, shared by all heads and serving
+is used as given.  With `out_gate` "sigmoid" the heads side by side are multiplied by sigmoid(W_g h) (tensor "g") before W_o.
+Only c and the rotated kr are cached: one row [c | kr] per position, shared by all heads and serving
 as key and as value (`CacheRequest(values_in_keys=True)`).  To attend over such rows a head's unrotated query is carried
 onto the latent, qa_h = W_uk,h^T q_h,unrot (so that qa_h . c = q_h,unrot . k_h), the attention runs with every head
 reading the same rows, its result per head is a weighted sum of latents, and W_uv,h turns that into the head's values.
@@ -31,7 +32,7 @@ from .linear import linear
 from .registry import lookup, register
 
 _DEFAULT_NAMES = {"dq": "mix.dq", "dq_norm": "mix.dq.norm", "uq": "mix.uq", "dkv": "mix.dkv", "dkv_norm": "mix.dkv.norm",
-                  "uk": "mix.uk", "uv": "mix.uv", "o": "mix.o"}
+                  "uk": "mix.uk", "uv": "mix.uv", "o": "mix.o", "g": "mix.g"}
 
 
 @register("mixer", "latent_attention")
@@ -47,6 +48,9 @@ class LatentAttention(Mixer):
         self.q_rank = int(params["q_rank"])
         self.scale = float(params["scale"])
         self.eps = float(params["eps"])
+        self.out_gate = params.get("out_gate")
+        if self.out_gate not in (None, "sigmoid"):
+            raise ValueError(f"out_gate must be None or \"sigmoid\", got {self.out_gate!r}")
         if min(self.n_heads, self.dim, self.v_dim, self.rank, self.q_rank) < 1 or self.rot_dim < 0:
             raise ValueError("latent attention: sizes must be positive")
         pos = params.get("position")
@@ -60,7 +64,8 @@ class LatentAttention(Mixer):
 
     def weights(self) -> List[WeightSpec]:
         n, H = self.names, self.n_heads
-        return [WeightSpec(n["dq"], (self.q_rank, self.hidden)), WeightSpec(n["dq_norm"], (self.q_rank,), "ones"),
+        gate = [WeightSpec(n["g"], (H * self.v_dim, self.hidden))] if self.out_gate else []
+        return gate + [WeightSpec(n["dq"], (self.q_rank, self.hidden)), WeightSpec(n["dq_norm"], (self.q_rank,), "ones"),
                 WeightSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
                 WeightSpec(n["dkv"], (self.rank + self.rot_dim, self.hidden)), WeightSpec(n["dkv_norm"], (self.rank,), "ones"),
                 WeightSpec(n["uk"], (H * self.dim, self.rank)), WeightSpec(n["uv"], (H * self.v_dim, self.rank)),
@@ -82,6 +87,7 @@ class LatentAttention(Mixer):
         del dq, dkv
         self.w_uq = rt.place(tensors[n["uq"]])
         self.w_o = rt.place(tensors[n["o"]])
+        self.w_g = rt.place(tensors[n["g"]]) if self.out_gate else None
         # per head: W_uk,h^T as [rank, dim] (rows of the carried query), W_uv,h as [v_dim, rank]
         self.w_uk_t = rt.place(tensors[n["uk"]]).view(H, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = rt.place(tensors[n["uv"]]).view(H, self.v_dim, self.rank).contiguous()
@@ -112,4 +118,6 @@ class LatentAttention(Mixer):
         with ops.bucket("out matmul"):
             att = torch.empty((T, H * self.v_dim), dtype=dt, device=h.device)
             ops.bmm_heads(att, self.v_dim, lat, self.rank, self.w_uv, self.v_dim, self.rank)
+            if self.out_gate:
+                att = ops.gate_mul(att, linear(h, self.w_g, out_dtype=dt), "sigmoid")
             linear(att, self.w_o, out=residual, accumulate=True)

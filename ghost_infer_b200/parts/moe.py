@@ -189,3 +189,85 @@ class ScoredExperts(FeedForward):
         with ops.bucket("ffn matmul"):
             ops.settle(residual)
             ops.moe_combine(residual, down, inv, wts if self.weight_on == "output" else None)
+
+
+@register("feed_forward", "share_routed_experts")
+class ShareRoutedExperts(FeedForward):
+    """Routed gated experts whose router scores every expert by its share of a softmax over ALL experts.
+
+    z = W_r h (32-bit); s = softmax(z) over all experts; the `top` experts with the largest s + `correction` (a stored vector,
+    one number per expert; it steers the choice only) are chosen; their weights are s (without the correction) divided by
+    the sum of the chosen shares (+ 1e-20), times `route_scale`.  An expert, and the shared expert that runs for every token
+    and is added as it is, computes W_down (g sigmoid(`alpha` g) (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h,
+    -limit, limit) (`limit` for the routed experts, `shared_limit` for the shared one; 0 or None: no clamps).  No biases.
+
+    Tensors: "mlp.router", "mlp.correction", "mlp.e<i>.{gate,up,down}", "mlp.shared.{gate,up,down}" unless
+    `params["tensor_names"]` replaces the stems "router", "correction", "expert" (a format with `{i}`) or "shared"."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["expert_ff"])
+        self.limit = float(params.get("limit") or 0.0)
+        self.alpha = float(params.get("alpha", 1.0))
+        self.route_scale = float(params.get("route_scale", 1.0))
+        self.has_correction = bool(params.get("correction", True))
+        self.shared_ff = int(params["shared_ff"]) if params.get("shared_ff") else None
+        self.shared_limit = float(params.get("shared_limit") or 0.0)
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"a token cannot use {self.top} of {self.experts} experts")
+        self.router_name = self.tensor_name("router", "mlp.router")
+        self.correction_name = self.tensor_name("correction", "mlp.correction")
+        self.expert_stem = self.tensor_name("expert", "mlp.e{i}.")
+        self.shared_stem = self.tensor_name("shared", "mlp.shared.")
+
+    def _expert(self, i: int, what: str) -> str:
+        return self.expert_stem.format(i=i) + what
+
+    def weights(self) -> List[WeightSpec]:
+        out = [WeightSpec(self.router_name, (self.experts, self.hidden))]
+        if self.has_correction:
+            out.append(WeightSpec(self.correction_name, (self.experts,)))
+        for i in range(self.experts):
+            out += [WeightSpec(self._expert(i, "gate"), (self.ff, self.hidden)), WeightSpec(self._expert(i, "up"), (self.ff, self.hidden)),
+                    WeightSpec(self._expert(i, "down"), (self.hidden, self.ff))]
+        if self.shared_ff:
+            s = self.shared_stem
+            out += [WeightSpec(s + "gate", (self.shared_ff, self.hidden)), WeightSpec(s + "up", (self.shared_ff, self.hidden)),
+                    WeightSpec(s + "down", (self.hidden, self.shared_ff))]
+        return out
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.w_router = rt.place(tensors[self.router_name])
+        # the correction joins 32-bit shares: kept as 32-bit values
+        self.correction = (tensors[self.correction_name].to(device=rt.device, dtype=torch.float32).contiguous()
+                           if self.has_correction else None)
+        # [E, 2 f, d]: gate rows, then up rows
+        self.w_gate_up = rt.place(torch.stack([torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0)
+                                               for i in range(self.experts)]))
+        self.w_down = rt.place(torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]))   # [E, d, f]
+        if self.w_gate_up.dtype != self.w_down.dtype:
+            self.w_gate_up, self.w_down = self.w_gate_up.float(), self.w_down.float()
+        if self.shared_ff:
+            s = self.shared_stem
+            g, u = rt.place(tensors[s + "gate"]), rt.place(tensors[s + "up"])
+            if g.dtype != u.dtype:
+                g, u = g.float(), u.float()
+            self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
+            self.w_shared_down = rt.place(tensors[s + "down"])
+
+    def forward(self, h, residual, step) -> None:
+        with ops.bucket("router"):
+            ids, wts = ops.moe_route_shares(h, self.w_router, self.top, self.correction, self.route_scale)
+            offsets, perm, inv = ops.moe_plan(ids, self.experts)
+        with ops.bucket("experts"):
+            down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top, False, self.limit, self.alpha)
+        with ops.bucket("ffn matmul"):
+            ops.settle(residual)
+            if self.shared_ff:
+                act = ops.clamped_glu(linear(h, self.w_shared_gu, out_dtype=self.rt.dtype), self.shared_limit, self.alpha)
+                linear(act, self.w_shared_down, out=residual, accumulate=True)
+            ops.moe_combine(residual, down, inv, wts)

@@ -84,6 +84,8 @@ class ModelSpec:
     ignorable_tensors: Tuple[str, ...] = ()     # names a weights file may carry although no part uses them
     embedding_norm: Optional[PartSpec] = None   # a norm on the embedded tokens, before the first layer (32-bit result)
     embedding_norm_prefix: str = "model.embed_norm."
+    streams: int = 0                            # > 0: the layers work on so many copies of the residual stream, side by side per
+                                                # token ([tokens, streams * width]); they start equal and are summed before the final norm
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):
