@@ -164,8 +164,26 @@ def route(h, W, pre, r):
     return ids, w
 
 
-def mixture(h, W, pre, mlp):
+def choice_gaps(h, W, pre, r):
+    """Per token, how far the last chosen expert's choice score lies above the first one left out, or, where leaving that
+    expert out would hardly matter (its share of the chosen ones' weight is below 3%), infinity; infinity too if all are chosen."""
+    z = h @ W[pre + "router"].T
+    s = np.exp(z - z.max(axis=1, keepdims=True))
+    s = s / s.sum(axis=1, keepdims=True)
+    c = s + W[pre + "correction"]
+    order = np.argsort(-c, axis=1, kind="stable")
+    top = r["top"]
+    if top >= c.shape[1]:
+        return np.full(h.shape[0], np.inf)
+    cs, ss = np.take_along_axis(c, order, axis=1), np.take_along_axis(s, order, axis=1)
+    matters = np.maximum(ss[:, top - 1], ss[:, top]) / (ss[:, :top].sum(axis=1) + 1e-20) >= 0.03
+    return np.where(matters, cs[:, top - 1] - cs[:, top], np.inf)
+
+
+def mixture(h, W, pre, mlp, gaps=None):
     ids, w = route(h, W, pre, mlp["router"])
+    if gaps is not None:
+        gaps.append(choice_gaps(h, W, pre, mlp["router"]))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, we in zip(ids[t], w[t]):
@@ -185,8 +203,9 @@ def hyper_sublayer(xs, W, lp, q, norm_w, eps, run):
     return mixed + W[f"{lp}hc{q}.out"][:, None, None] * y[None]
 
 
-def forward(cfg, W, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence from its first token (float64); optionally the summed streams after every layer."""
+def forward(cfg, W, tokens, return_layers=False, gaps=None):
+    """Logits [T, vocab] of one sequence from its first token (float64); optionally the summed streams after every layer.
+    `gaps` (a list): receives every routed layer's `choice_gaps`, so that a test can tell where a rounding could flip a choice."""
     W = {k: np.asarray(v, dtype=np.float64) for k, v in W.items()}
     eps = cfg["norm"]["eps"]
     T = len(tokens)
@@ -210,7 +229,66 @@ def forward(cfg, W, tokens, return_layers=False):
 
         xs = hyper_sublayer(xs, W, lp, 1, W[lp + "norm1"], eps, mixer)
         if layer.get("mlp") is not None:
-            xs = hyper_sublayer(xs, W, lp, 2, W[lp + "norm2"], eps, lambda h: mixture(h, W, lp + "mlp.", layer["mlp"]))
+            xs = hyper_sublayer(xs, W, lp, 2, W[lp + "norm2"], eps, lambda h: mixture(h, W, lp + "mlp.", layer["mlp"], gaps))
         after.append(xs.sum(axis=0))
     logits = (rms_unit(xs.sum(axis=0), eps) * W["final.norm"]) @ W["head"].T * cfg["logit_scale"]
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def bf16_values(a):
+    """Rounds to the nearest bfloat16 value (ties to even), kept as float64: a bfloat16 file then holds the weights exactly."""
+    f = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+    u = f.view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return u.view(np.float32).astype(np.float64).reshape(np.shape(a))
+
+
+def random_weights(cfg, seed=0):
+    """Weights for `cfg` (name -> float64 array of bfloat16 values)."""
+    rng = np.random.default_rng(seed)
+    d, S, out = int(cfg["width"]), int(cfg["streams"]), {}
+    taps = int(cfg["canon"]["taps"])
+
+    def put(name, shape, std=None, mean=0.0):
+        std = std if std is not None else (1.0 / math.sqrt(shape[-1]) if len(shape) > 1 else 0.5)
+        out[name] = bf16_values(rng.standard_normal(shape) * std + mean)
+
+    put("embed", (int(cfg["vocab"]), d), 1.0); put("embed.norm", (d,), 0.1, 1.0)
+    put("final.norm", (d,), 0.1, 1.0); put("head", (int(cfg["vocab"]), d))
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, kind = f"l{i}.", layer["mixer"], layer["type"]
+        subs = (1, 2) if layer.get("mlp") is not None else (1,)
+        for q in subs:
+            put(f"{p}norm{q}", (d,), 0.1, 1.0)
+            put(f"{p}hc{q}.in", (S,), 0.3, 0.6); put(f"{p}hc{q}.out", (S,), 0.3, 0.8)
+            out[f"{p}hc{q}.mix"] = bf16_values(np.eye(S) * 0.9 + rng.standard_normal((S, S)) * 0.15)
+            put(f"{p}canon{q}", (d, taps), 0.4); put(f"{p}rg{q}", (d, d)); put(f"{p}rg{q}.b", (d,), 0.5, 0.5)
+        x = p + "mix."
+        if kind == "attention":
+            H, G, n, mv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+            put(x + "q", (H * n, d)); put(x + "q.b", (H * n,), 0.3); put(x + "q.norm", (n,), 0.2, 1.3)
+            put(x + "sink", (H,), 1.0); put(x + "g", (H, d)); put(x + "o", (d, H * mv)); put(x + "o.b", (d,), 0.2)
+            if m.get("kv_from") is None:
+                put(x + "k", (G * n, d)); put(x + "k.b", (G * n,), 0.3); put(x + "k.norm", (n,), 0.2, 1.3)
+                put(x + "v", (G * mv, d)); put(x + "v.b", (G * mv,), 0.3)
+        elif kind == "latent_attention":
+            H, n, r, mv, rank, qr = (int(m[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
+            put(x + "dq", (qr, d)); put(x + "dq.norm", (qr,), 0.1, 1.0); put(x + "uq", (H * (n + r), qr))
+            put(x + "dkv", (rank + r, d)); put(x + "dkv.norm", (rank,), 0.1, 1.0); put(x + "uk", (H * n, rank))
+            put(x + "uv", (H * mv, rank)); put(x + "g", (H * mv, d)); put(x + "o", (d, H * mv))
+        else:
+            H, n, mv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+            put(x + "q", (H * n, d)); put(x + "k", (H * n, d)); put(x + "v", (H * mv, d)); put(x + "g", (H * mv, d))
+            put(x + "o", (d, H * mv)); put(x + "norm", (H * mv,), 0.1, 1.0)
+            put(x + "i", (H, d), 2.0 / math.sqrt(d)); put(x + "i.b", (H,), 1.0); put(x + "f", (H, d), 2.0 / math.sqrt(d)); put(x + "f.b", (H,), 1.0, 2.0)
+        if layer.get("mlp") is not None:
+            f, y = layer["mlp"], p + "mlp."
+            E = int(f["router"]["experts"])
+            put(y + "router", (E, d), 3.0 / math.sqrt(d)); put(y + "correction", (E,), 0.1)
+            for e in range(E):
+                put(f"{y}e{e}.gate", (int(f["expert"]["ff"]), d), 2.0 / math.sqrt(d)); put(f"{y}e{e}.up", (int(f["expert"]["ff"]), d), 2.0 / math.sqrt(d))
+                put(f"{y}e{e}.down", (d, int(f["expert"]["ff"])))
+            if f.get("shared") is not None:
+                sf = int(f["shared"]["ff"])
+                put(y + "shared.gate", (sf, d), 2.0 / math.sqrt(d)); put(y + "shared.up", (sf, d), 2.0 / math.sqrt(d)); put(y + "shared.down", (d, sf))
+    return out
