@@ -197,6 +197,38 @@ NUZINEX_SIZES = {
 }
 
 
+def _torutar(width, heads, kv, dim, vdim, window, keep_first, lat_heads, lat_dim, lat_rot, lat_vdim, kv_rank, q_rank, mem_heads, mem_dim,
+             mem_vdim, experts, top, expert_ff, shared_ff, streams, taps, vocab, **_):
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.0}, "expert": {"ff": expert_ff, "limit": 7.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    own = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window, "keep_first": keep_first},
+           "rot": {"base": 250000.0, "dims": dim // 2}}
+    latent = {"heads": lat_heads, "dim": lat_dim, "rot_dim": lat_rot, "vdim": lat_vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+              "scale": (lat_dim + lat_rot) ** -0.5, "rot": {"base": 500000.0, "dims": lat_rot}}
+    memory = {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": 15.0}
+    layers = [{"type": "latent_attention", "mixer": latent, "mlp": mlp}, {"type": "mlstm", "mixer": memory, "mlp": mlp},
+              {"type": "attention", "mixer": own, "mlp": mlp}, {"type": "attention", "mixer": dict(own, kv_from=2), "mlp": mlp}]
+    return {"architecture": "Torutar", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "streams": streams, "canon": {"taps": taps},
+            "logit_scale": 1.0, "layers": layers}
+
+
+# layer sizes of the kind real models have: latent attention, a matrix memory, windowed attention that keeps its first
+# positions, and a layer that reads that one's keys and values, each with routed experts and a shared one, over several copies
+# of the stream.  Beside it the hybrid decoder (capped attention with a sink, state-space layers, dense and routed
+# feed-forwards) and the Llama decoder at the same width, heads and feed-forward width
+TORUTAR_SIZES = {
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, vdim=64, window=1024, keep_first=64, lat_heads=16, lat_dim=128, lat_rot=64,
+                  lat_vdim=128, kv_rank=512, q_rank=1536, mem_heads=16, mem_dim=64, mem_vdim=128, experts=16, top=2, expert_ff=2048,
+                  shared_ff=2048, streams=4, taps=4, vocab=32000, chunk=1024, ff=8192, ssm_heads=64, ssm_dim=64, state=128, groups=8, pairs=2),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, window=2048, keep_first=128, lat_heads=32, lat_dim=128, lat_rot=64,
+                  lat_vdim=128, kv_rank=512, q_rank=1536, mem_heads=32, mem_dim=64, mem_vdim=128, experts=16, top=2, expert_ff=4096,
+                  shared_ff=4096, streams=4, taps=4, vocab=32000, chunk=2048, ff=14336, ssm_heads=128, ssm_dim=64, state=128, groups=8, pairs=2),
+    "w2048_odd": dict(width=2048, heads=24, kv=4, dim=64, vdim=40, window=500, keep_first=20, lat_heads=32, lat_dim=64, lat_rot=32,
+                      lat_vdim=64, kv_rank=256, q_rank=768, mem_heads=12, mem_dim=96, mem_vdim=64, experts=32, top=4, expert_ff=1024,
+                      shared_ff=2048, streams=2, taps=3, vocab=32000, chunk=500, ff=6144, ssm_heads=64, ssm_dim=40, state=96, groups=4, pairs=2),
+}
+
+
 def _barovik_beside(z):
     keys = ("width", "heads", "kv", "dim", "vdim", "chunk", "ff", "ssm_heads", "ssm_dim", "state", "groups", "experts", "top",
             "expert_ff", "shared_ff", "vocab", "pairs")
@@ -204,7 +236,7 @@ def _barovik_beside(z):
 
 
 def measure_hybrid(args):
-    """`--workload barovik` / `--workload navalorn` / `--workload nuzinex`: prompt and decode throughput of that decoder at a few real layer sizes
+    """`--workload barovik` / `--workload navalorn` / `--workload nuzinex` / `--workload torutar`: prompt and decode throughput of that decoder at a few real layer sizes
     (random weights), beside the Llama decoder with the same width, heads, feed-forward width and number of layers (nuzinex:
     beside the hybrid decoder with windowed attention and state-space layers, and the Llama decoder); and the
     device time per kind of operation for one prompt step and one decode step of each.  One JSON line."""
@@ -289,12 +321,14 @@ def measure_hybrid(args):
     sizes, build, label = (LATENT_SIZES, _navalorn, "navalorn") if latent else (HYBRID_SIZES, _barovik, "barovik")
     if args.workload == "nuzinex":
         sizes, build, label = NUZINEX_SIZES, _nuzinex, "nuzinex"
+    if args.workload == "torutar":
+        sizes, build, label = TORUTAR_SIZES, _torutar, "torutar"
     names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     for name in names:
         z = sizes[name]
         hybrid = one(build(**z))
         out[name] = {"sizes": z, label: hybrid}
-        if label == "nuzinex" and not args.skip_points:
+        if label in ("nuzinex", "torutar") and not args.skip_points:
             out[name]["barovik_equal_size"] = one(_barovik_beside(z))
         if not args.skip_points:
             out[name]["llama_equal_size"] = one(_llama_like(z["width"], z["heads"], z["kv"], z["llama_dim"] if latent else z["dim"], z["ff"],
@@ -440,10 +474,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik", "navalorn", "nuzinex"],
-                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik, navalorn, nuzinex: the hybrid decoder, or the "
-                         "decoder with a latent cache, beside the Llama decoder at equal layer sizes (--sizes, --batch, --held)")
-    ap.add_argument("--sizes", default="", help="for --workload barovik / navalorn / nuzinex: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik", "navalorn", "nuzinex", "torutar"],
+                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik, navalorn, nuzinex, torutar: one of the "
+                         "other decoders beside the Llama decoder at equal layer sizes (--sizes, --batch, --held)")
+    ap.add_argument("--sizes", default="", help="for --workload barovik / navalorn / nuzinex / torutar: which of its sizes to run, with commas (default: all)")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
@@ -466,7 +500,7 @@ def main():
         for kv in filter(None, args.tune.split(",")):
             k, v = kv.split("=")
             _ops.TUNE[k] = type(_ops.TUNE[k])(float(v))
-    if args.workload in ("barovik", "navalorn", "nuzinex"):
+    if args.workload in ("barovik", "navalorn", "nuzinex", "torutar"):
         return measure_hybrid(args)
     if args.workload != "8b":
         return run_workload(args.workload, args)

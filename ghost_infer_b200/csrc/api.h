@@ -527,6 +527,19 @@ int gi_moe_route_shares(int* ids, float* wts, float* sgate, const void* h, int d
 int gi_moe_gemm_gate_up_clamped(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
                                 const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
                                 int interleaved, float limit, float alpha, void* stream);
+// gi_attn_decode_kr_ex / gi_attn_prefill_tc_ex with a window that keeps the sequence's first `keep_first` positions visible.
+int gi_attn_decode_kr_ex2(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                          const void* vcache, const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                          int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits, int own_tiles, int hdv,
+                          float softcap, const float* sinks, int chunk, int keep_first, void* stream);
+int gi_attn_prefill_tc_ex2(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,
+                           const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
+                           const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale,
+                           int window, int hdv, float softcap, const float* sinks, int chunk, int keep_first, void* stream);
+int gi_attn_prefill_t5_ex2(void* out, long ldo, const void* q, long ldq, long q_rows, long q_cols, const void* kcache,
+                           const void* vcache, long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens,
+                           const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
+                           float scale, int window, float softcap, const float* sinks, int chunk, int keep_first, void* stream);
 // The plain attention kernels with a window that keeps the sequence's first `keep_first` positions visible as well.
 int gi_attn_prefill_generic_ex3(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
                                 const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,

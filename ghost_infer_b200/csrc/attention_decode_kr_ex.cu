@@ -30,7 +30,7 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
                       const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slots,
                       const int* __restrict__ seq_lens, int n_heads, int n_kv, float scale, int window, int n_splits,
-                      int own_tiles, int hd, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk) {
+                      int own_tiles, int hd, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk, int keep_first) {
   constexpr int CH = HD / 8, CHV = HDV / 8;      // 16-byte chunks per row
   constexpr int TILE_BYTES = KT * HD * 2;        // one K tile
   constexpr int VTILE_BYTES = KT * HDV * 2;      // one V tile
@@ -59,7 +59,10 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
   if (window > 0) t_first = max(0, len - window);
   if (pos_chunk > 0) t_first = max(t_first, ((len - 1) / pos_chunk) * pos_chunk);
   const int t_base = (t_first / KT) * KT;
-  const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
+  // a window may keep the sequence's first `keep_first` positions visible: their tiles are counted before the window's own
+  const int kept = window > 0 ? keep_first : 0;
+  const int kept_tiles = min((kept + KT - 1) / KT, t_base / KT);
+  const int tiles = kept_tiles + (len > t_base ? (len - t_base + KT - 1) / KT : 0);
   const int per = own_tiles > 0 ? own_tiles : (tiles + n_splits - 1) / n_splits;
   const int used = per > 0 ? max(1, (tiles + per - 1) / per) : 1;      // slices of this sequence that hold keys
   const int tile_lo = sp * per, tile_hi = min(tiles, tile_lo + per);
@@ -80,7 +83,7 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
   const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * 1.4426950408889634f;
 
   auto issue = [&](int tile, int stage) {
-    const int t0 = t_base + tile * KT;
+    const int t0 = tile < kept_tiles ? tile * KT : t_base + (tile - kept_tiles) * KT;
     const int page = slot >= 0 ? gi::ld_step(block_table + (size_t)slot * max_pages + t0 / PAGE_TOKENS) : 0;
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS);
     unsigned char* ks = my_ring + (size_t)stage * STAGE_BYTES;
@@ -90,14 +93,14 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
       const int idx = i * 32 + lane;
       const int r = idx / CH, c = idx % CH;
       // rows outside the visible span and the padding columns are zero-filled, not read
-      const int ok = (t0 + r < len && t0 + r >= t_first && c * 8 < hd) ? 16 : 0;
+      const int ok = (t0 + r < len && (t0 + r >= t_first || t0 + r < kept) && c * 8 < hd) ? 16 : 0;
       gi::cp_async_16(gi::smem_u32(ks + gi::swz<CH>(r, c)), kcache + (row0 + (ok ? r : 0)) * hd + (ok ? c * 8 : 0), ok);
     }
 #pragma unroll
     for (int i = 0; i < KT * CHV / 32; ++i) {
       const int idx = i * 32 + lane;
       const int r = idx / CHV, c = idx % CHV;
-      const int ok = (t0 + r < len && t0 + r >= t_first && c * 8 < hdv) ? 16 : 0;
+      const int ok = (t0 + r < len && (t0 + r >= t_first || t0 + r < kept) && c * 8 < hdv) ? 16 : 0;
       gi::cp_async_16(gi::smem_u32(vs + gi::swz<CHV>(r, c)), vcache + (row0 + (ok ? r : 0)) * hdv + (ok ? c * 8 : 0), ok);
     }
   };
@@ -151,7 +154,7 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
     __syncwarp();
     const unsigned char* ks = my_ring + (size_t)stage * STAGE_BYTES;
     const unsigned char* vs = ks + TILE_BYTES;
-    const int t0 = t_base + tile * KT;
+    const int t0 = tile < kept_tiles ? tile * KT : t_base + (tile - kept_tiles) * KT;
 
     // S^T = K Q^T: rows are the tile's 16 keys
     float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -163,7 +166,7 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
       gi::mma_16816(s, ka, qb[kk >> 1][(kk & 1) * 2], qb[kk >> 1][(kk & 1) * 2 + 1]);
     }
     // mask (two keys per thread) and running softmax (two heads per thread)
-    const bool ok0 = t0 + g < len && t0 + g >= t_first, ok1 = t0 + g + 8 < len && t0 + g + 8 >= t_first;
+    const bool ok0 = t0 + g < len && (t0 + g >= t_first || t0 + g < kept), ok1 = t0 + g + 8 < len && (t0 + g + 8 >= t_first || t0 + g + 8 < kept);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const float sc = softcap > 0.f ? cap_out * gi::tanh_fast(s[c] * cap_in) : s[c] * sl2;
@@ -277,7 +280,7 @@ template <int HD, int HDV, int WARPS, int STAGES>
 int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, float* pml, const __nv_bfloat16* q, long ldq,
            const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int max_pages, const int* slots, const int* lens,
            int H, int KV, float scale, int window, int n_splits, int own_tiles, int hd, int hdv, float softcap, const float* sinks,
-           int chunk) {
+           int chunk, int keep_first) {
   constexpr size_t ring = (size_t)WARPS * STAGES * (KT * HD * 2 + KT * HDV * 2);
   constexpr size_t merge = (size_t)(WARPS * COLS * (HDV + 8) + 2 * WARPS * COLS) * sizeof(float);
   constexpr size_t smem = COLS * HD * 2 + (ring > merge ? ring : merge);
@@ -290,7 +293,7 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, float* po, f
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(kern, grid, dim3(WARPS * 32), smem, s, out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV,
-                              scale, window, n_splits, own_tiles, hd, hdv, softcap, sinks, chunk),
+                              scale, window, n_splits, own_tiles, hd, hdv, softcap, sinks, chunk, keep_first),
                    "attention decode (keys on rows, general)");
 }
 
@@ -303,7 +306,18 @@ extern "C" int gi_attn_decode_kr_ex(void* out, long ldo, float* part_o, float* p
                                     const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                                     float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
                                     const float* sinks, int chunk, void* stream) {
+  return gi_attn_decode_kr_ex2(out, ldo, part_o, part_ml, q, ldq, kcache, vcache, block_table, max_pages, seq_slots, seq_lens, n_seqs,
+                               n_heads, n_kv, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, 0, stream);
+}
+
+// The same with a window that keeps the sequence's first `keep_first` positions visible as well.
+extern "C" int gi_attn_decode_kr_ex2(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                     const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                                     const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                                     float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
+                                     const float* sinks, int chunk, int keep_first, void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return gi::fail(GI_ERR_ARG, "attention: kept first positions go with a window, not with chunks");
   if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (hd <= 0 || hd > 128 || hd % 8 || hdv <= 0 || hdv > 128 || hdv % 8)
     return gi::fail(GI_ERR_UNSUPPORTED, "attention decode (keys on rows): key size %d, value size %d; multiples of 8 up to 128", hd, hdv);
@@ -323,7 +337,7 @@ extern "C" int gi_attn_decode_kr_ex(void* out, long ldo, float* part_o, float* p
 #define GI_DECODE_KRX(HD_, HDV_, W_)                                                                                          \
   rc = launch<HD_, HDV_, W_, 2>(grid, s, (__nv_bfloat16*)out, ldo, part_o, part_ml, (const __nv_bfloat16*)q, ldq,              \
                                 (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, max_pages, seq_slots, \
-                                seq_lens, n_heads, n_kv, scale, window, n_splits, own_tiles, hd, hdv, softcap, sinks, chunk)
+                                seq_lens, n_heads, n_kv, scale, window, n_splits, own_tiles, hd, hdv, softcap, sinks, chunk, keep_first)
   if (hd <= 64 && hdv <= 64) GI_DECODE_KRX(64, 64, 6);
   else if (hd <= 64) GI_DECODE_KRX(64, 128, 4);
   else if (hdv <= 64) GI_DECODE_KRX(128, 64, 4);

@@ -81,7 +81,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long ldo,
                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv, float scale,
-                       int window, int q_tiles, int paired, float softcap, const float* __restrict__ sinks, int chunk) {
+                       int window, int q_tiles, int paired, float softcap, const float* __restrict__ sinks, int chunk, int keep_first) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF;
   // instruction descriptors: float accumulator, bfloat16 operands, M 128; S = Q K^T has N 64 and both operands K-major,
@@ -170,14 +170,18 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
   if (chunk > 0) t_first = max(t_first, ((pos0 + q0) / chunk) * chunk);     // chunks of positions: see the row warps
   const int kt_begin = (t_first / BKV) * BKV;
-  const int n_tiles = (p_last - kt_begin) / BKV + 1;
+  // a window may keep the sequence's first `keep_first` positions visible: their tiles (whole pages, which such a cache never
+  // gives back) come before the window's own
+  const int kept = window > 0 ? keep_first : 0;
+  const int kept_tiles = min((kept + BKV - 1) / BKV, kt_begin / BKV);
+  const int n_tiles = kept_tiles + (p_last - kt_begin) / BKV + 1;
 
   // Two threads issue the products, each with its own loads, so that neither chain waits behind the other's
   // barriers: S(j+1) = Q K(j+1)^T wants only the keys and the score buffer back (the rows of S(j) read into
   // registers), O += P(j) V(j) wants the probabilities staged.  One thread for both spent half a tile's time in
   // the one chain's waits while the other chain was ready.
   auto row_of = [&](int tile) {        // where a tile's keys and values lie: the page comes from the sequence's page table
-    const int kt = kt_begin + tile * BKV;
+    const int kt = tile < kept_tiles ? tile * BKV : kt_begin + (tile - kept_tiles) * BKV;
     const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
     return (page * n_kv + kvh) * PAGE_TOKENS;
   };
@@ -281,7 +285,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
-      const int kt = kt_begin + j * BKV;
+      const int kt = j < kept_tiles ? j * BKV : kt_begin + (j - kept_tiles) * BKV;
       ok = mbar_wait(s_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
       if (!ok) break;
       tc_fence_after();
@@ -293,7 +297,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // scores -> probabilities.  A tile every row of the block sees in full needs no mask: one maximum, then one
       // fused multiply-add, one exponential and one addition per score.  Tiles on the diagonal (or at a window's
       // edge) take the masked path.
-      const bool interior = (kt + BKV - 1 <= pos0 + q0) && kt >= t_first && (window <= 0 || kt > pos0 + q0 + BQ - 1 - window) &&
+      const bool interior = (kt + BKV - 1 <= pos0 + q0) && ((kt >= t_first && (window <= 0 || kt > pos0 + q0 + BQ - 1 - window)) || kt + BKV <= kept) &&
                             kt >= c_lo_last;
       if (softcap > 0.f) {
 #pragma unroll
@@ -314,7 +318,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = kt + q * 32 + c;
-            const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window) && key >= c_lo_row;
+            const bool vis = key <= p_row && (key >= t_first || key < kept) && (window <= 0 || key > p_row - window || key < kept) && key >= c_lo_row;
             const float v = vis ? __uint_as_float(sr[q][c]) : -INFINITY;
             sr[q][c] = __float_as_uint(v);
             tmax = fmaxf(tmax, v * sl2);
@@ -367,7 +371,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_wait_st();
       // keys of this tile that no row of the block may see (past the block's last position, or before every window)
       // get zero values: their probabilities are zero, but zero times a stale non-number would still be a non-number
-      const int lo = max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);
+      const int lo = j < kept_tiles ? 0 : max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);      // a kept tile holds written positions only
       if (lo > 0 || hi < BKV) {
         ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
         if (!ok) break;
@@ -440,7 +444,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out,
               long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
-              int n_heads, int n_kv, float scale, int window, int q_tiles, int paired, float softcap, const float* sinks, int chunk) {
+              int n_heads, int n_kv, float scale, int window, int q_tiles, int paired, float softcap, const float* sinks, int chunk, int keep_first) {
   constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + 12 * 8 + 16;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
   int dev;
@@ -450,7 +454,7 @@ int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUten
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(attn_prefill_t5_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, out, ldo, block_table, max_pages,
-                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk),
+                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk, keep_first),
                    "attention prefill (tcgen05)");
 }
 
@@ -471,7 +475,21 @@ extern "C" int gi_attn_prefill_t5_ex(void* out, long ldo, const void* q, long ld
                                      const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
                                      int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, float softcap,
                                      const float* sinks, int chunk, void* stream) {
+  return gi_attn_prefill_t5_ex2(out, ldo, q, ldq, q_rows, (long)(n_heads + 2 * n_kv) * hd, kcache, vcache, cache_pages, block_table,
+                                max_pages, cu_seqlens, seq_slots, seq_pos0, n_seqs, max_q_len, n_heads, n_kv, hd, scale, window, softcap,
+                                sinks, chunk, 0, stream);
+}
+
+// The same with the width of the query rows given (rows that hold the queries alone: n_heads * hd) and a window that keeps
+// the sequence's first `keep_first` positions visible as well.
+extern "C" int gi_attn_prefill_t5_ex2(void* out, long ldo, const void* q, long ldq, long q_rows, long q_cols, const void* kcache,
+                                      const void* vcache, long cache_pages, const int* block_table, int max_pages,
+                                      const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                      int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, float softcap,
+                                      const float* sinks, int chunk, int keep_first, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return gi::fail(GI_ERR_ARG, "attention: kept first positions go with a window, not with chunks");
+  if (q_cols < (long)n_heads * hd) return gi::fail(GI_ERR_ARG, "attention: query rows of %ld numbers cannot hold %d heads", q_cols, n_heads);
   if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): head size %d, only 64 and 128", hd);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
@@ -480,7 +498,7 @@ extern "C" int gi_attn_prefill_t5_ex(void* out, long ldo, const void* q, long ld
     return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): rows must be 16-byte aligned");
   if (n_seqs > 65535 || (max_q_len + BQ - 1) / BQ > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or query tiles in one launch");
   CUtensorMap mq, mk, mv;
-  int rc = gi::tensor_map_2d_ex(&mq, q, q_rows, (long)(n_heads + 2 * n_kv) * hd, ldq, GI_BF16, 64, BQ);
+  int rc = gi::tensor_map_2d_ex(&mq, q, q_rows, q_cols, ldq, GI_BF16, 64, BQ);
   if (rc != GI_OK) return rc;
   const long cache_rows = cache_pages * n_kv * PAGE_TOKENS;
   if (cache_rows > 0x7fffffffL || q_rows > 0x7fffffffL)       // TMA coordinates are 32-bit
@@ -499,9 +517,9 @@ extern "C" int gi_attn_prefill_t5_ex(void* out, long ldo, const void* q, long ld
   dim3 grid(n_heads, n_seqs, paired ? (q_tiles + 1) / 2 : q_tiles);
   if (hd == 128)
     return launch_t5<128>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                          seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk);
+                          seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk, keep_first);
   return launch_t5<64>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                       seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk);
+                       seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk, keep_first);
 }
 
 // Query tiles two to a block: 0 never, 1 where the launch then is one round of blocks (default), 2 always; for

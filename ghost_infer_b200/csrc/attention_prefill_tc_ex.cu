@@ -25,7 +25,7 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv,
                        float scale, int window, int q_tiles, int hd, int hdv, float softcap, const float* __restrict__ sinks,
-                       int chunk) {
+                       int chunk, int keep_first) {
   constexpr int CH = HD / 8, CHV = HDV / 8;
   constexpr int TILE_BYTES = BKV * HD * 2, VTILE_BYTES = BKV * HDV * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -47,10 +47,13 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
   if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
   if (chunk > 0) t_first = max(t_first, ((pos0 + q0) / chunk) * chunk);
   const int kt_begin = (t_first / BKV) * BKV;
-  const int n_tiles = (p_last - kt_begin) / BKV + 1;
+  // a window may keep the sequence's first `keep_first` positions visible: their tiles come before the window's own
+  const int kept = window > 0 ? keep_first : 0;
+  const int kept_tiles = min((kept + BKV - 1) / BKV, kt_begin / BKV);
+  const int n_tiles = kept_tiles + (p_last - kt_begin) / BKV + 1;
 
   auto issue_kv = [&](int tile, int stage) {
-    const int kt = kt_begin + tile * BKV;
+    const int kt = tile < kept_tiles ? tile * BKV : kt_begin + (tile - kept_tiles) * BKV;
     const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS;
     unsigned char* ks = kv_s + (size_t)stage * STAGE_BYTES;
@@ -60,14 +63,14 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
       const int idx = i * WARPS * 32 + tid;
       const int r = idx / CH, c = idx % CH;
       // rows nobody here sees and the padding columns: zeros, not read
-      const int ok = (kt + r <= p_last && kt + r >= t_first && c * 8 < hd) ? 16 : 0;
+      const int ok = (kt + r <= p_last && (kt + r >= t_first || kt + r < kept) && c * 8 < hd) ? 16 : 0;
       gi::cp_async_16(gi::smem_u32(ks + gi::swz<CH>(r, c)), kcache + (row0 + (ok ? r : 0)) * hd + (ok ? c * 8 : 0), ok);
     }
 #pragma unroll
     for (int i = 0; i < BKV * CHV / (WARPS * 32); ++i) {
       const int idx = i * WARPS * 32 + tid;
       const int r = idx / CHV, c = idx % CHV;
-      const int ok = (kt + r <= p_last && kt + r >= t_first && c * 8 < hdv) ? 16 : 0;
+      const int ok = (kt + r <= p_last && (kt + r >= t_first || kt + r < kept) && c * 8 < hdv) ? 16 : 0;
       gi::cp_async_16(gi::smem_u32(vs + gi::swz<CHV>(r, c)), vcache + (row0 + (ok ? r : 0)) * hdv + (ok ? c * 8 : 0), ok);
     }
   };
@@ -116,11 +119,11 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
         gi::ldmatrix_x4(qf[ks], gi::smem_u32(q_s + gi::swz<CH>(r, c)));
       }
     }
-    const int kt = kt_begin + tile * BKV;
+    const int kt = tile < kept_tiles ? tile * BKV : kt_begin + (tile - kept_tiles) * BKV;
     const unsigned char* ks_ = kv_s + (size_t)stage * STAGE_BYTES;
     const unsigned char* vs_ = ks_ + TILE_BYTES;
     // a warp whose rows all lie before this tile, or whose windows all ended before it, has nothing to do here
-    const bool active = kt <= p_warp_last && (window <= 0 || kt + BKV - 1 > p_warp_last - 15 - window) && kt + BKV - 1 >= c_lo_warp;
+    const bool active = kt <= p_warp_last && (window <= 0 || kt + BKV - 1 > p_warp_last - 15 - window || kt < kept) && kt + BKV - 1 >= c_lo_warp;
     if (active) {
       float s[BKV / 8][4];
 #pragma unroll
@@ -143,7 +146,7 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
         for (int c = 0; c < 4; ++c) {
           const int key = kt + nt * 8 + 2 * t + (c & 1);
           const int p = p_row0 + (c >> 1) * 8;
-          const bool ok = key <= p && p <= p_last && (window <= 0 || key > p - window) && key >= c_lo[c >> 1];
+          const bool ok = key <= p && p <= p_last && (window <= 0 || key > p - window || key < kept) && key >= c_lo[c >> 1];
           const float sc = softcap > 0.f ? cap_out * gi::tanh_fast(s[nt][c] * cap_in) : s[nt][c] * sl2;
           s[nt][c] = ok ? sc : -INFINITY;
           tmax[c >> 1] = fmaxf(tmax[c >> 1], s[nt][c]);
@@ -223,7 +226,7 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
 template <int HD, int HDV>
 int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, const __nv_bfloat16* q, long ldq, const __nv_bfloat16* kc,
            const __nv_bfloat16* vc, const int* bt, int max_pages, const int* cu, const int* slots, const int* pos0, int H, int KV,
-           float scale, int window, int q_tiles, int hd, int hdv, float softcap, const float* sinks, int chunk) {
+           float scale, int window, int q_tiles, int hd, int hdv, float softcap, const float* sinks, int chunk, int keep_first) {
   constexpr size_t smem = (size_t)BQ * HD * 2 + 2 * ((size_t)BKV * HD * 2 + (size_t)BKV * HDV * 2);
   auto kern = attn_prefill_tcx_kernel<HD, HDV>;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
@@ -234,7 +237,7 @@ int launch(dim3 grid, cudaStream_t s, __nv_bfloat16* out, long ldo, const __nv_b
     if (dev >= 0) configured[dev] = true;
   }
   kern<<<grid, WARPS * 32, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, scale, window, q_tiles, hd, hdv,
-                                      softcap, sinks, chunk);
+                                      softcap, sinks, chunk, keep_first);
   return gi::check_launch("attention prefill (tensor cores, general)");
 }
 
@@ -245,7 +248,18 @@ extern "C" int gi_attn_prefill_tc_ex(void* out, long ldo, const void* q, long ld
                                      const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                                      float scale, int window, int hdv, float softcap, const float* sinks, int chunk,
                                      void* stream) {
+  return gi_attn_prefill_tc_ex2(out, ldo, q, ldq, kcache, vcache, block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_seqs,
+                                max_q_len, n_heads, n_kv, hd, scale, window, hdv, softcap, sinks, chunk, 0, stream);
+}
+
+// The same with a window that keeps the sequence's first `keep_first` positions visible as well.
+extern "C" int gi_attn_prefill_tc_ex2(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,
+                                      const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
+                                      const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
+                                      float scale, int window, int hdv, float softcap, const float* sinks, int chunk,
+                                      int keep_first, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return gi::fail(GI_ERR_ARG, "attention: kept first positions go with a window, not with chunks");
   if (hd <= 0 || hd > 128 || hd % 8 || hdv <= 0 || hdv > 128 || hdv % 8)
     return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tensor cores): key size %d, value size %d; multiples of 8 up to 128", hd, hdv);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
@@ -260,7 +274,7 @@ extern "C" int gi_attn_prefill_tc_ex(void* out, long ldo, const void* q, long ld
 #define GI_TCX(HDP, HDVP)                                                                                                  \
   return launch<HDP, HDVP>(grid, s, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kcache,   \
                            (const __nv_bfloat16*)vcache, block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads,  \
-                           n_kv, scale, window, q_tiles, hd, hdv, softcap, sinks, chunk)
+                           n_kv, scale, window, q_tiles, hd, hdv, softcap, sinks, chunk, keep_first)
   if (hd <= 64 && hdv <= 64) GI_TCX(64, 64);
   if (hd <= 64) GI_TCX(64, 128);
   if (hdv <= 64) GI_TCX(128, 64);

@@ -62,6 +62,8 @@ def _bind():
         "gi_attn_prefill_t5": [P, L, P, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_prefill_t5_status": [P],
         "gi_attn_prefill_t5_ex": [P, L, P, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, F, P, I, P],
+        "gi_attn_prefill_t5_ex2": [P, L, P, L, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, F, P, I, I, P],
+        "gi_attn_prefill_tc_ex2": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, I, P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
@@ -75,6 +77,7 @@ def _bind():
         "gi_attn_decode_generic_ex": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
         "gi_attn_prefill_tc_ex": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
         "gi_attn_decode_kr_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
+        "gi_attn_decode_kr_ex2": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, I, P],
         "gi_kv_store": [P, I, L, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv": [P, P, I, L, P, P, I, P, L, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv_update": [P, I, L, P, L, I, P, P, I, I, I, I, I, P],
@@ -942,22 +945,23 @@ def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                     cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                     max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                     window: Optional[int], out: torch.Tensor, *, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                    chunk: Optional[int] = None) -> torch.Tensor:
+                    chunk: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
     """As attn_prefill_generic, for bfloat16 and head size 64 or 128 (keys and values alike), on tcgen05 tensor cores with
-    TMA-fed operands.  `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries).
-    `softcap`, `sinks`, `chunk`: as `attn_prefill_generic`'s."""
+    TMA-fed operands.  `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries), or
+    rows of the queries alone.  `softcap`, `sinks`, `chunk`, `keep_first`: as `attn_prefill_generic`'s."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 prefill attention takes bfloat16 queries, cache and output")
-    if not kcache.is_contiguous() or not vcache.is_contiguous() or q.shape[1] != (n_heads + 2 * n_kv) * head_dim:
-        raise KernelError("the tcgen05 prefill attention takes the packed q/k/v rows and contiguous cache pages")
-    _check(lib, lib.gi_attn_prefill_t5_ex(
-        out.data_ptr(), ldo, q.data_ptr(), ldq, q.shape[0], kcache.data_ptr(), vcache.data_ptr(), kcache.shape[0],
+    if not kcache.is_contiguous() or not vcache.is_contiguous() or q.shape[1] not in ((n_heads + 2 * n_kv) * head_dim, n_heads * head_dim):
+        raise KernelError("the tcgen05 prefill attention takes the packed q/k/v rows (or the queries alone) and contiguous cache pages")
+    _check(lib, lib.gi_attn_prefill_t5_ex2(
+        out.data_ptr(), ldo, q.data_ptr(), ldq, q.shape[0], q.shape[1], kcache.data_ptr(), vcache.data_ptr(), kcache.shape[0],
         _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
         _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-        float(scale), int(window or 0), float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()))
+        float(scale), int(window or 0), float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), int(keep_first or 0),
+        _stream()))
     return out
 
 
@@ -1327,29 +1331,26 @@ def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, 
             _cuda(qkv, "queries")
             if qkv.dtype != torch.bfloat16 or memory.k.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
                 raise KernelError("the tensor-core decode attention takes bfloat16 queries, cache and output")
-            _check(lib, lib.gi_attn_decode_kr_ex(
+            _check(lib, lib.gi_attn_decode_kr_ex2(
                 out.data_ptr(), _rows(out, "attention output"), part_o.data_ptr() if part_o is not None else None,
                 part_ml.data_ptr() if part_ml is not None else None, qkv.data_ptr(), _rows(qkv, "queries"), memory.k.data_ptr(),
                 memory.v.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
                 _i32(step.seq_slots, "slots"), _i32(step.seq_lens, "lengths"), step.n_seqs, n_heads, n_kv, head_dim, float(scale),
                 int(window or 0), int(n_splits), int(own_tiles), v_dim, float(softcap or 0.0), _sinks_ptr(sinks, n_heads),
-                int(chunk or 0), _stream()), 2 if n_splits > 1 else 1)
+                int(chunk or 0), keep_first, _stream()), 2 if n_splits > 1 else 1)
             return out
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
                                    n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
                                    **opts)
-    if keep_first:
-        # TENSOR-CORE-KEPT-FIRST
-        return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
-                                    step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, **opts)
     if (TUNE["attn_general_tc"] and TUNE["attn_prefill_tcgen05"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16
             and head_dim == v_dim and head_dim in (64, 128) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
-            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
+            and qkv.shape[1] in ((n_heads + 2 * n_kv) * head_dim, n_heads * head_dim)
             and memory.k.is_contiguous() and memory.v.is_contiguous()):
         # keys and values of one of the two sizes the tcgen05 kernel takes: scores and output in tensor memory
         return attn_prefill_t5(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
                                step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, softcap=softcap,
-                               sinks=sinks, chunk=chunk)
+                               sinks=sinks, chunk=chunk, keep_first=keep_first)
     if (TUNE["attn_general_tc"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16 and head_dim % 8 == 0
             and v_dim % 8 == 0 and head_dim <= 128 and v_dim <= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
             and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
@@ -1364,7 +1365,7 @@ def attn_prefill_tc_general(q: torch.Tensor, kcache: torch.Tensor, vcache: torch
                             cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                             max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float, window: Optional[int],
                             out: torch.Tensor, *, v_dim: Optional[int] = None, softcap: float = 0.0,
-                            sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+                            sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
     """`attn_prefill_generic` with its options on tensor cores: bfloat16, key and value sizes multiples of 8 up to 128."""
     lib = _bind()
     _cuda(q, "queries")
@@ -1373,11 +1374,11 @@ def attn_prefill_tc_general(q: torch.Tensor, kcache: torch.Tensor, vcache: torch
         raise KernelError("the tensor-core prefill attention takes bfloat16 queries, cache and output")
     if not kcache.is_contiguous() or not vcache.is_contiguous():
         raise KernelError("the tensor-core prefill attention takes contiguous cache pages")
-    _check(lib, lib.gi_attn_prefill_tc_ex(
+    _check(lib, lib.gi_attn_prefill_tc_ex2(
         out.data_ptr(), ldo, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"),
         block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"), _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"),
         n_seqs, max_q_len, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(v_dim or head_dim),
-        float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()))
+        float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), int(keep_first or 0), _stream()))
     return out
 
 
@@ -1397,11 +1398,13 @@ def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_head
     whatever else the step holds."""
     limit = window or chunk
     keep_first = int(keep_first or 0) if window else 0
-    if head_dim is not None and attn_general_tc_ok(dtype, head_dim, v_dim or head_dim) and not keep_first:
-        seen = min(max_kv_len, int(limit) + 15) if limit else max_kv_len
+    if head_dim is not None and attn_general_tc_ok(dtype, head_dim, v_dim or head_dim):
+        # what a token can see: the window (or chunk) and, in whole tiles of 16, the kept first positions
+        reach = int(limit) + (keep_first + 15) // 16 * 16 if limit else None
+        seen = min(max_kv_len, reach + 15) if limit else max_kv_len
         lens = [min(int(n), seen) for n in kv_lens] if kv_lens else None
         n_splits, own = attn_decode_plan(n_seqs, seen, sm_count, n_heads, n_kv, 64 if max(head_dim, v_dim or head_dim) <= 64 else 128,
-                                         limit, torch.bfloat16, lens)
+                                         reach, torch.bfloat16, lens)
         return "tensor cores", n_splits, own
     span = max_kv_len
     for limit in (window, chunk):
