@@ -540,6 +540,13 @@ int gi_attn_prefill_t5_ex2(void* out, long ldo, const void* q, long ldq, long q_
                            const void* vcache, long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens,
                            const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                            float scale, int window, float softcap, const float* sinks, int chunk, int keep_first, void* stream);
+// gi_gemm_tc_bf16's gated mode with the clamped form of the gated value (see gi_clamped_glu); W's gate and up rows interleaved
+// in blocks of 8.  And a prompt step's clamped gated experts through it, stretch by stretch (see gi_moe_experts_tc).
+int gi_gemm_tc_bf16_clamped(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo, int tile_n,
+                            float limit, float alpha, void* stream);
+int gi_moe_experts_tc_clamped(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                              const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
+                              float limit, float alpha, float* scratch, int* counters, int n_counters, void* stream);
 // The plain attention kernels with a window that keeps the sequence's first `keep_first` positions visible as well.
 int gi_attn_prefill_generic_ex3(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
                                 const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,

@@ -371,14 +371,15 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_wait_st();
       // keys of this tile that no row of the block may see (past the block's last position, or before every window)
       // get zero values: their probabilities are zero, but zero times a stale non-number would still be a non-number
-      const int lo = j < kept_tiles ? 0 : max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);      // a kept tile holds written positions only
-      if (lo > 0 || hi < BKV) {
+      const int lo = max(0, t_first - kt), hi = min(BKV, p_last + 1 - kt);
+      const int lo_kept = min(lo, max(0, kept - kt));      // of the rows before every window, the first lo_kept are kept first positions: seen
+      if (lo > lo_kept || hi < BKV) {
         ok = mbar_wait(v_full0 + 8 * s, (uint32_t)((j >> 1) & 1), 3, &g_attn_status);
         if (!ok) break;
         unsigned char* vt = v_s + s * KV_BYTES;
         for (int idx = threadIdx.x; idx < BKV * (HD / 8); idx += 128) {
           const int r = idx / (HD / 8), cidx = idx % (HD / 8);   // key row, 16-byte chunk of the row (its halves lie apart)
-          if (r < lo || r >= hi) *reinterpret_cast<uint4*>(vt + (cidx / 8) * KV_HALF + r * 128 + (cidx % 8) * 16) = make_uint4(0, 0, 0, 0);
+          if ((r < lo && r >= lo_kept) || r >= hi) *reinterpret_cast<uint4*>(vt + (cidx / 8) * KV_HALF + r * 128 + (cidx % 8) * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

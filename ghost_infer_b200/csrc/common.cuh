@@ -81,6 +81,16 @@ __device__ __forceinline__ float gated_mul_bf16(float g, float u, int act) {
   return act ? gelu_tanh_mul_bf16(g, u) : silu_mul_bf16(g, u);
 }
 
+// The clamped form of a gated value for the same epilogues: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// g' sigmoid(alpha g') (u' + 1), with the approximate exponential and division.
+__device__ __forceinline__ float clamped_glu_bf16(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * alpha * -1.4426950408889634f));
+  return __fdividef(g, 1.0f + e) * (u + 1.0f);
+}
+
 // tanh for the capped scores of the 16-bit attention kernels: 1 - 2 / (e^(2x) + 1) with the approximate exponential and
 // division (absolute error about 1e-7, far below what the rounding of queries and keys to 8 bits leaves in a score; the
 // ends are right: +1 for large x, -1 for large -x).  The 32-bit path uses tanhf.

@@ -47,7 +47,9 @@ struct TilePlan {
   int n_tiles;       // all tiles
   int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form); the bfloat16 store's: 2 relu squared,
                      // 3 gelu in its exact (erf) form
+                     // 3 gelu in its exact (erf) form; the gated epilogue's again: 4 the clamped form (see gi::clamped_glu_bf16)
   const __nv_bfloat16* bias;   // added to the sums before the bfloat16 store's activation (one per output column), or null
+  float limit, alpha;          // of the clamped form
 };
 
 // What the q/k/v product's epilogue needs to rotate and store by itself (mode GI_TC_QKV_ROPE): the output's columns are
@@ -300,7 +302,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int j = 0; j < 8; j += 2) {
                 const float g0 = __uint_as_float(r[blk * 16 + j]), g1 = __uint_as_float(r[blk * 16 + j + 1]);
                 const float u0 = __uint_as_float(r[blk * 16 + 8 + j]), u1 = __uint_as_float(r[blk * 16 + 8 + j + 1]);
-                __nv_bfloat162 v = __floats2bfloat162_rn(gi::gated_mul_bf16(g0, u0, plan.act), gi::gated_mul_bf16(g1, u1, plan.act));
+                __nv_bfloat162 v = plan.act == 4 ? __floats2bfloat162_rn(gi::clamped_glu_bf16(g0, u0, plan.limit, plan.alpha), gi::clamped_glu_bf16(g1, u1, plan.limit, plan.alpha))
+                                                 : __floats2bfloat162_rn(gi::gated_mul_bf16(g0, u0, plan.act), gi::gated_mul_bf16(g1, u1, plan.act));
                 p[j / 2] = *reinterpret_cast<uint32_t*>(&v);
               }
               stage_chunk(stg, row, q * 2 + blk, make_uint4(p[0], p[1], p[2], p[3]));
@@ -495,10 +498,26 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   return gi_gemm_tc_bf16_bias(out, mode, A, W, nullptr, M, N, K, lda, ldw, ldo, tile_n, stream);
 }
 
+static int gemm_tc_any(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K, long lda, long ldw,
+                       long ldo, int tile_n, float limit, float alpha, void* stream);
+
 extern "C" int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K,
                                     long lda, long ldw, long ldo, int tile_n, void* stream) {
+  return gemm_tc_any(out, mode, A, W, bias, M, N, K, lda, ldw, ldo, tile_n, 0.f, 1.f, stream);
+}
+
+// The gated product (mode GI_TC_SWIGLU's layout of W and of the output) with the clamped form of the gated value:
+// min(g, limit) * sigmoid(alpha * that) * (clamp(u, -limit, limit) + 1).
+extern "C" int gi_gemm_tc_bf16_clamped(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo,
+                                       int tile_n, float limit, float alpha, void* stream) {
+  if (!(limit > 0.f)) return gi::fail(GI_ERR_ARG, "tensor-core product: the clamped form needs a positive limit");
+  return gemm_tc_any(out, GI_TC_SWIGLU, A, W, nullptr, M, N, K, lda, ldw, ldo, tile_n, limit, alpha, stream);
+}
+
+static int gemm_tc_any(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K, long lda, long ldw,
+                       long ldo, int tile_n, float limit, float alpha, void* stream) {
   const bool relu2 = (mode & GI_ACT_RELU2) != 0, gelu_erf = (mode & GI_ACT_GELU_ERF) != 0;
-  const int act = relu2 ? 2 : (gelu_erf ? 3 : ((mode & GI_ACT_GELU) ? 1 : 0));
+  const int act = limit > 0.f ? 4 : (relu2 ? 2 : (gelu_erf ? 3 : ((mode & GI_ACT_GELU) ? 1 : 0)));
   mode &= 0xff;
   if ((relu2 || gelu_erf) ? (mode != GI_TC_STORE_BF16 || (relu2 && gelu_erf)) : (act && mode != GI_TC_SWIGLU))
     return gi::fail(GI_ERR_ARG, "tensor-core product: an activation without the mode that applies it");
@@ -527,6 +546,8 @@ extern "C" int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const vo
   TilePlan plan = g_tail_tiles ? plan_tiles(M, N, tile_n, gran, sm_count()) : plan_tiles(M, N, tile_n, gran, 0);
   plan.act = act;
   plan.bias = (const __nv_bfloat16*)bias;
+  plan.limit = limit;
+  plan.alpha = alpha;
   CUtensorMap mw2 = mw;
   if (plan.narrow > 0) {
     rc = gi::tensor_map_2d(&mw2, W, N, K, ldw, plan.narrow);

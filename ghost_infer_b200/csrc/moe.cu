@@ -602,7 +602,16 @@ extern "C" int gi_moe_gather_rows_scaled(void* out, const void* in, int dtype, l
 // streamed product, longer ones the tiled one.  One call per layer, so that the host's share is the launches alone.
 static int experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                       const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
-                      float* scratch, int* counters, int n_counters, void* stream, bool ungated);
+                      float* scratch, int* counters, int n_counters, void* stream, bool ungated, float limit = 0.f, float alpha = 1.f);
+
+// The same for gated experts in the clamped form (limit > 0; see gi_clamped_glu): every stretch takes the tiled product.
+extern "C" int gi_moe_experts_tc_clamped(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                                         const void* w_down, long down_stride, const int* host_offsets, int experts, int width,
+                                         int f, float limit, float alpha, float* scratch, int* counters, int n_counters, void* stream) {
+  if (!(limit > 0.f)) return gi::fail(GI_ERR_ARG, "experts on tensor cores: the clamped form needs a positive limit");
+  return experts_tc(out, hidden, rows, w_gate_up, gate_up_stride, w_down, down_stride, host_offsets, experts, width, f, scratch,
+                    counters, n_counters, stream, false, limit, alpha);
+}
 
 extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                                  const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
@@ -622,7 +631,7 @@ extern "C" int gi_moe_experts_tc_ungated(float* out, void* hidden, const void* r
 
 static int experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                       const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
-                      float* scratch, int* counters, int n_counters, void* stream, bool ungated) {
+                      float* scratch, int* counters, int n_counters, void* stream, bool ungated, float limit, float alpha) {
   if (experts <= 0 || width <= 0 || f <= 0 || f % 8 != 0 || width % 8 != 0)
     return gi::fail(GI_ERR_UNSUPPORTED, "experts on tensor cores: width %d and hidden width %d must be multiples of 8", width, f);
   const __nv_bfloat16* a = (const __nv_bfloat16*)rows;
@@ -637,7 +646,7 @@ static int experts_tc(float* out, void* hidden, const void* rows, const void* w_
   static bool made[gi::MAX_DEVICES_SEEN] = {false};
   int dev = -1;
   bool many = false;
-  const int small = ungated ? 0 : 64;      // stretches of up to this many rows take the streamed product (gated experts only)
+  const int small = (ungated || limit > 0.f) ? 0 : 64;      // stretches of up to this many rows take the streamed product (silu-gated experts only)
   const int up_rows = ungated ? f : 2 * f;
   for (int e = 0; e < experts; ++e) many = many || host_offsets[e + 1] - host_offsets[e] > small;
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
@@ -664,8 +673,10 @@ static int experts_tc(float* out, void* hidden, const void* rows, const void* w_
     // narrower tiles where wide ones would leave most SMs without one
     const int row_tiles = (m + 127) / 128;
     const int tile_up = row_tiles * ((up_rows + 255) / 256) < 64 ? 128 : 256, tile_down = row_tiles * ((width + 255) / 256) < 64 ? 128 : 256;
-    int rc = gi_gemm_tc_bf16(h + (size_t)lo * f, ungated ? (GI_TC_STORE_BF16 | GI_ACT_RELU2) : GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m,
-                             up_rows, width, width, width, f, tile_up, s);
+    int rc = limit > 0.f ? gi_gemm_tc_bf16_clamped(h + (size_t)lo * f, a + (size_t)lo * width, wgu, m, up_rows, width, width, width, f, tile_up,
+                                                   limit, alpha, s)
+                         : gi_gemm_tc_bf16(h + (size_t)lo * f, ungated ? (GI_TC_STORE_BF16 | GI_ACT_RELU2) : GI_TC_SWIGLU, a + (size_t)lo * width,
+                                           wgu, m, up_rows, width, width, width, f, tile_up, s);
     if (rc == GI_OK)
       rc = gi_gemm_tc_bf16(out + (size_t)lo * width, GI_TC_STORE_F32, h + (size_t)lo * f, wd, m, width, f, f, f, width, tile_down, s);
     if (rc != GI_OK) return rc;

@@ -88,6 +88,7 @@ def _bind():
         "gi_moe_gemm_gate_up": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, I, P],
         "gi_moe_gather_rows": [P, P, I, L, P, I, I, I, P],
         "gi_moe_experts_tc": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
+        "gi_moe_experts_tc_clamped": [P, P, P, P, L, P, L, P, I, I, I, F, F, P, P, I, P],
         "gi_moe_gemm_down": [P, P, I, L, P, I, L, P, I, I, I, I, P],
         "gi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
         "gi_moe_route_scored": [P, P, P, P, I, L, P, P, I, I, I, I, I, I, P],
@@ -1607,10 +1608,11 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     return down
 
 
-def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, host_offsets) -> torch.Tensor:
+def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, host_offsets, limit: float = 0.0,
+                          alpha: float = 1.0) -> torch.Tensor:
     """The experts' outputs, float32 [entries, width], for rows already in sorted order, through the tcgen05 products expert
     by expert; `host_offsets`: the experts' offsets as Python integers (the caller has read them back).  bfloat16, gate and
-    up rows interleaved in blocks of 8."""
+    up rows interleaved in blocks of 8.  `limit` > 0: the clamped form of the gated value (see `moe_experts`)."""
     lib = _bind()
     _cuda(rows, "sorted rows")
     experts, f2, width = w_gate_up.shape
@@ -1628,6 +1630,12 @@ def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: t
     scratch, counters = _stream_buffers(rows.device)
     offs = (c_int * (experts + 1))(*[int(x) for x in host_offsets])
     n_live = sum(1 for a, b in zip(host_offsets, host_offsets[1:]) if b > a)
+    if limit and limit > 0:
+        _check(lib, lib.gi_moe_experts_tc_clamped(out.data_ptr(), hidden.data_ptr(), rows.data_ptr(), w_gate_up.data_ptr(),
+                                                  w_gate_up.stride(0), w_down.data_ptr(), w_down.stride(0), offs, experts, width, f,
+                                                  float(limit), float(alpha), scratch.data_ptr(), counters.data_ptr(), counters.numel(),
+                                                  _stream()), 2 * n_live)
+        return out
     _check(lib, lib.gi_moe_experts_tc(out.data_ptr(), hidden.data_ptr(), rows.data_ptr(), w_gate_up.data_ptr(), w_gate_up.stride(0),
                                       w_down.data_ptr(), w_down.stride(0), offs, experts, width, f, scratch.data_ptr(),
                                       counters.data_ptr(), counters.numel(), _stream()), 2 * n_live)

@@ -245,12 +245,22 @@ class ShareRoutedExperts(FeedForward):
         # the correction joins 32-bit shares: kept as 32-bit values
         self.correction = (tensors[self.correction_name].to(device=rt.device, dtype=torch.float32).contiguous()
                            if self.has_correction else None)
-        # [E, 2 f, d]: gate rows, then up rows
-        self.w_gate_up = rt.place(torch.stack([torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0)
-                                               for i in range(self.experts)]))
+        # [E, 2 f, d]: gate rows, then up rows; on the 16-bit path in blocks [8 gate | 8 up], as the tensor-core product's gated
+        # epilogue wants them (the plain kernels read either layout)
+        self.interleaved = rt.dtype == torch.bfloat16 and self.ff % 8 == 0 and rt.device.type == "cuda"
+        gate_up = []
+        for i in range(self.experts):
+            g, u = tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]
+            if self.interleaved:
+                gate_up.append(torch.stack([g.reshape(self.ff // 8, 8, self.hidden), u.reshape(self.ff // 8, 8, self.hidden)], dim=1)
+                               .reshape(2 * self.ff, self.hidden))
+            else:
+                gate_up.append(torch.cat([g, u], dim=0))
+        self.w_gate_up = rt.place(torch.stack(gate_up))
         self.w_down = rt.place(torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]))   # [E, d, f]
         if self.w_gate_up.dtype != self.w_down.dtype:
             self.w_gate_up, self.w_down = self.w_gate_up.float(), self.w_down.float()
+        self.interleaved = self.interleaved and self.w_gate_up.dtype == torch.bfloat16
         if self.shared_ff:
             s = self.shared_stem
             g, u = rt.place(tensors[s + "gate"]), rt.place(tensors[s + "up"])
@@ -259,12 +269,25 @@ class ShareRoutedExperts(FeedForward):
             self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
             self.w_shared_down = rt.place(tensors[s + "down"])
 
+    # rows per expert, on average, from which a prompt step takes the tensor-core products expert by expert
+    ROWS_FOR_TENSOR_CORES = 96
+
+    def _by_expert(self, h, step) -> bool:
+        return (self.interleaved and self.limit > 0 and not step.is_decode and h.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                and h.shape[0] * self.top >= self.ROWS_FOR_TENSOR_CORES * self.experts and not torch.cuda.is_current_stream_capturing())
+
     def forward(self, h, residual, step) -> None:
         with ops.bucket("router"):
             ids, wts = ops.moe_route_shares(h, self.w_router, self.top, self.correction, self.route_scale)
             offsets, perm, inv = ops.moe_plan(ids, self.experts)
         with ops.bucket("experts"):
-            down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top, False, self.limit, self.alpha)
+            if self._by_expert(h, step):
+                # enough rows per expert: the host reads the experts' offsets back (one wait) and every expert's stretch goes
+                # through the products the dense layers use, the clamped gate in the first one's epilogue
+                rows = ops.moe_gather_rows(h, perm, self.top)
+                down = ops.moe_experts_by_expert(rows, self.w_gate_up, self.w_down, offsets.cpu().tolist(), self.limit, self.alpha)
+            else:
+                down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top, self.interleaved, self.limit, self.alpha)
         with ops.bucket("ffn matmul"):
             ops.settle(residual)
             if self.shared_ff:
