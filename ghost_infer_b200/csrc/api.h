@@ -489,6 +489,10 @@ int gi_stream_sum(float* out, const float* x, const int* rows, int n_rows, int s
 // h[t] = rmsnorm(sum_s blend[s] x[t][s]) * w in `dtype`; `zero` (or null): float32 [tokens][d] set to zero in the same pass.
 int gi_hyper_read(void* h, int dtype, const float* x, const float* blend, const void* w, int w_dtype, float* zero, int n_tokens,
                   int streams, int d, float eps, void* stream);
+// gi_hyper_read and, for a step of one token a sequence, the input convolution in the same launch (conv_out, or null).
+int gi_hyper_read_conv(void* h, int dtype, const float* x, const float* blend, const void* w, int w_dtype, float* zero, int n_tokens,
+                       int streams, int d, float eps, void* conv_out, const void* taps_w, int k_dtype, const float* state,
+                       long state_ld, int state_rows, const int* slots, int taps, void* stream);
 // out[t] = h[t] + sum_j taps_w[:, j] h[t - taps + 1 + j] per channel (taps_w [d][taps]); inputs before the step come from the
 // sequence's state (float32 [taps - 1][d] per slot, oldest first; rows state_ld apart, the last row serves slot -1).  Rows of
 // one sequence are neighbours in the step and carry the same slot.

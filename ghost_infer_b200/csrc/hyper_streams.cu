@@ -25,6 +25,9 @@ constexpr int MAX_STREAMS = 16;
 constexpr int MAX_TAPS = 8;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+template <typename T> __device__ __forceinline__ float rounded(float v);
+template <> __device__ __forceinline__ float rounded<float>(float v) { return v; }
+template <> __device__ __forceinline__ float rounded<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 __global__ void stream_expand_kernel(float* __restrict__ x, const float* __restrict__ e, int S, int d, size_t total) {
   gi::pdl_prologue();
@@ -143,6 +146,143 @@ hyper_write_kernel(float* x, const float* y, const T* z, const TW* __restrict__ 
   }
 }
 
+
+// ---- the same three kernels, four neighbouring channels a thread, 16 bytes a load: for widths that are multiples of 4 and
+// rows that start on 16-byte boundaries.  A row's sums are formed in an order that follows from the width alone here too.
+
+// hyper_read; with `conv_out` the input convolution as well, for steps of one token a sequence (every older input comes from
+// the sequence's state): c = h + sum of taps, h rounded to the activation type first, as the separate kernel reads it.
+template <typename TO, typename TW, typename TK>
+__global__ void __launch_bounds__(256)
+hyper_read4_kernel(TO* __restrict__ h, const float* x, const float* __restrict__ a, const TW* __restrict__ w, float* __restrict__ zero,
+                   int S, int d, float eps, TO* __restrict__ conv_out, const TK* __restrict__ k, const float* state, long state_ld,
+                   int state_rows, const int* slots, int taps) {
+  extern __shared__ __align__(16) float u[];
+  __shared__ float scratch[33];
+  gi::pdl_prologue();
+  const size_t t = blockIdx.x;
+  const float* xr = x + t * S * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < d; c += 1024) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < S; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)s * d + c);
+      const float as = a[s];
+      acc.x = fmaf(as, v.x, acc.x); acc.y = fmaf(as, v.y, acc.y); acc.z = fmaf(as, v.z, acc.z); acc.w = fmaf(as, v.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(u + c) = acc;
+    ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+  }
+  // (a thread's share of the row's sum is four neighbouring channels here, every 256th in the plain kernel: the two kernels
+  // differ by rounding; which of them runs follows from the width and the alignment alone, never from the step)
+  const float rs = 1.0f / sqrtf(gi::block_sum(ss, scratch) / (float)d + eps);
+  const float* st = nullptr;
+  if (conv_out != nullptr && taps > 1) {
+    const int slot = slots[t];
+    st = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld;
+  }
+  for (int c = threadIdx.x * 4; c < d; c += 1024) {
+    const float4 uv = *reinterpret_cast<const float4*>(u + c);
+    const float4 wv = gi::ld4(w + c);
+    float4 hv = make_float4(uv.x * rs * wv.x, uv.y * rs * wv.y, uv.z * rs * wv.z, uv.w * rs * wv.w);
+    gi::st4(h + t * d + c, hv);
+    if (zero != nullptr) *reinterpret_cast<float4*>(zero + t * d + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (conv_out != nullptr) {
+      float own[4] = {hv.x, hv.y, hv.z, hv.w};
+      float out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        own[e] = rounded<TO>(own[e]);       // as the stored row holds it
+        float acc = own[e];
+        for (int j = 0; j < taps; ++j) {
+          const float v = j == taps - 1 ? own[e] : st[(size_t)j * d + c + e];
+          acc = fmaf(gi::ldf(k + (size_t)(c + e) * taps + j), v, acc);
+        }
+        out[e] = acc;
+      }
+      gi::st4(conv_out + t * d + c, make_float4(out[0], out[1], out[2], out[3]));
+    }
+  }
+}
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+input_conv4_kernel(T* __restrict__ out, const T* h, const TW* __restrict__ k, const float* state, long state_ld, int state_rows,
+                   const int* slots, int d, int taps) {
+  gi::pdl_prologue();
+  const int t = blockIdx.x;
+  const int slot = slots[t];
+  const int q = rows_before(slots, t, taps - 1);
+  const float* st = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld;
+  for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < d; c += gridDim.y * 1024) {
+    const float4 o4 = gi::ld4(h + (size_t)t * d + c);
+    const float own[4] = {o4.x, o4.y, o4.z, o4.w};
+    float acc[4] = {own[0], own[1], own[2], own[3]};
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      float4 v4 = o4;
+      if (back > 0) v4 = back <= q ? gi::ld4(h + (size_t)(t - back) * d + c) : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - back + q) * d + c);
+      const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = fmaf(gi::ldf(k + (size_t)(c + e) * taps + j), v[e], acc[e]);
+    }
+    gi::st4(out + (size_t)t * d + c, make_float4(acc[0], acc[1], acc[2], acc[3]));
+  }
+}
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+hyper_write4_kernel(float* x, const float* y, const T* z, const TW* __restrict__ zb, const float* __restrict__ M,
+                    const float* __restrict__ o, const T* h, float* state, long state_ld, int state_rows, const int* slots,
+                    int n_tokens, int S, int d, int taps) {
+  gi::pdl_prologue();
+  const int t = blockIdx.x;
+  float* xr = x + (size_t)t * S * d;
+  for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < d; c += gridDim.y * 1024) {
+    float4 v = *reinterpret_cast<const float4*>(y + (size_t)t * d + c);
+    if (z != nullptr) {
+      const float4 g = gi::ld4(z + (size_t)t * d + c);
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (zb != nullptr) b = gi::ld4(zb + c);
+      v.x *= sigmoid_f(g.x + b.x); v.y *= sigmoid_f(g.y + b.y); v.z *= sigmoid_f(g.z + b.z); v.w *= sigmoid_f(g.w + b.w);
+    }
+    float4 old[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; ++s)
+      if (s < S) old[s] = *reinterpret_cast<const float4*>(xr + (size_t)s * d + c);
+    for (int to = 0; to < S; ++to) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) {
+          const float m = M[s * S + to];
+          acc.x = fmaf(m, old[s].x, acc.x); acc.y = fmaf(m, old[s].y, acc.y); acc.z = fmaf(m, old[s].z, acc.z); acc.w = fmaf(m, old[s].w, acc.w);
+        }
+      const float sh = o[to];
+      acc.x = fmaf(sh, v.x, acc.x); acc.y = fmaf(sh, v.y, acc.y); acc.z = fmaf(sh, v.z, acc.z); acc.w = fmaf(sh, v.w, acc.w);
+      *reinterpret_cast<float4*>(xr + (size_t)to * d + c) = acc;
+    }
+  }
+  if (state == nullptr || taps <= 1) return;
+  const int slot = slots[t];
+  if (t + 1 < n_tokens && slots[t + 1] == slot) return;       // not the sequence's last token of this step
+  const int q = rows_before(slots, t, taps - 1);
+  float* st = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld;
+  for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < d; c += gridDim.y * 1024) {
+    float4 keep[MAX_TAPS - 1];
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS - 1; ++i) {
+      if (i < taps - 1) {
+        const int back = taps - 2 - i;
+        keep[i] = back <= q ? gi::ld4(h + (size_t)(t - back) * d + c) : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - back + q) * d + c);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS - 1; ++i)
+      if (i < taps - 1) *reinterpret_cast<float4*>(st + (size_t)i * d + c) = keep[i];
+  }
+}
+
 __global__ void scale_rows_kernel(float* x, float c, size_t total) {
   gi::pdl_prologue();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -152,6 +292,9 @@ __global__ void scale_rows_kernel(float* x, float c, size_t total) {
 inline unsigned blocks_of(size_t total) { return (unsigned)((total + 255) / 256); }
 // few tokens: a row's channels over several blocks
 inline unsigned col_blocks(int n_tokens, int d) { return n_tokens >= 128 ? 1u : (unsigned)min(16, (d + 255) / 256); }
+// four channels a thread: every thread one group of four where the row is not longer than 64 blocks' worth
+inline unsigned col_blocks4(int d) { return (unsigned)max(1, min(64, (d + 1023) / 1024)); }
+inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 }  // namespace
 
@@ -173,11 +316,37 @@ extern "C" int gi_stream_sum(float* out, const float* x, const int* rows, int n_
 
 extern "C" int gi_hyper_read(void* h, int dtype, const float* x, const float* blend, const void* w, int w_dtype, float* zero,
                              int n_tokens, int streams, int d, float eps, void* stream) {
+  return gi_hyper_read_conv(h, dtype, x, blend, w, w_dtype, zero, n_tokens, streams, d, eps, nullptr, nullptr, GI_F32, nullptr, 0, 0,
+                            nullptr, 0, stream);
+}
+
+// The same and, for a step of one token a sequence, the input convolution in the same launch: conv_out = h + sum of taps,
+// the older inputs from the state (see gi_input_conv).  Needs a width that is a multiple of 4 and 16-byte aligned rows.
+extern "C" int gi_hyper_read_conv(void* h, int dtype, const float* x, const float* blend, const void* w, int w_dtype, float* zero,
+                                  int n_tokens, int streams, int d, float eps, void* conv_out, const void* taps_w, int k_dtype,
+                                  const float* state, long state_ld, int state_rows, const int* slots, int taps, void* stream) {
   if (n_tokens <= 0) return GI_OK;
+  const bool vec = d % 4 == 0 && aligned16(h) && aligned16(x) && aligned16(w) && aligned16(zero) && aligned16(conv_out) &&
+                   aligned16(state) && state_ld % 4 == 0;
+  if (conv_out != nullptr) {
+    if (!vec) return gi::fail(GI_ERR_UNSUPPORTED, "hyper_read: the convolution in the same launch needs a width that is a multiple of 4 and aligned rows");
+    if (taps < 1 || taps > MAX_TAPS || taps_w == nullptr || slots == nullptr || (taps > 1 && (state == nullptr || state_ld < (long)(taps - 1) * d)))
+      return gi::fail(GI_ERR_ARG, "hyper_read: the convolution needs 1 to %d taps, its weights, the slots and its state", MAX_TAPS);
+  }
   if (streams < 1 || streams > MAX_STREAMS || d < 1) return gi::fail(GI_ERR_UNSUPPORTED, "hyper_read: %d copies of the stream (at most %d)", streams, MAX_STREAMS);
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 200 * 1024) return gi::fail(GI_ERR_UNSUPPORTED, "hyper_read: rows of %d values are wider than shared memory", d);
   cudaError_t e = cudaSuccess;
+  if (vec) {
+    GI_DISPATCH_DTYPE(dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW, GI_DISPATCH_DTYPE(k_dtype, TK, {
+      auto kern = hyper_read4_kernel<TO, TW, TK>;
+      if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess)
+        e = gi::launch(kern, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (TO*)h, x, blend, (const TW*)w, zero, streams, d, eps,
+                       (TO*)conv_out, (const TK*)taps_w, state, state_ld, state_rows, slots, taps);
+    })));
+    return gi::check(e, "hyper_read");
+  }
   GI_DISPATCH_DTYPE(dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW, {
     auto kern = hyper_read_kernel<TO, TW>;
     if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -193,6 +362,12 @@ extern "C" int gi_input_conv(void* out, const void* h, int dtype, const void* ta
   if (taps < 1 || taps > MAX_TAPS || d < 1) return gi::fail(GI_ERR_UNSUPPORTED, "input_conv: %d taps (1 to %d)", taps, MAX_TAPS);
   if (taps > 1 && (state == nullptr || state_ld < (long)(taps - 1) * d)) return gi::fail(GI_ERR_ARG, "input_conv: no room for the last inputs");
   cudaError_t e = cudaSuccess;
+  if (d % 4 == 0 && aligned16(out) && aligned16(h) && aligned16(state) && state_ld % 4 == 0) {
+    GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+        e = gi::launch(input_conv4_kernel<T, TW>, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                       (const T*)h, (const TW*)taps_w, state, state_ld, state_rows, slots, d, taps)));
+    return gi::check(e, "input_conv");
+  }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(input_conv_kernel<T, TW>, dim3(n_tokens, col_blocks(n_tokens, d)), dim3(256), 0, (cudaStream_t)stream, (T*)out,
                      (const T*)h, (const TW*)taps_w, state, state_ld, state_rows, slots, d, taps)));
@@ -207,6 +382,13 @@ extern "C" int gi_hyper_write(float* x, const float* y, const void* z, const voi
   if (state != nullptr && (taps < 1 || taps > MAX_TAPS || h == nullptr || state_ld < (long)(taps - 1) * d))
     return gi::fail(GI_ERR_ARG, "hyper_write: the convolution's state needs 1 to %d taps, the inputs and room for them", MAX_TAPS);
   cudaError_t e = cudaSuccess;
+  if (d % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(z) && aligned16(z_bias) && aligned16(h) && aligned16(state) && state_ld % 4 == 0) {
+    GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+        e = gi::launch(hyper_write4_kernel<T, TW>, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, x, y,
+                       (const T*)z, (const TW*)z_bias, mix, share, (const T*)h, state, state_ld, state_rows, slots, n_tokens, streams, d,
+                       taps)));
+    return gi::check(e, "hyper_write");
+  }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(hyper_write_kernel<T, TW>, dim3(n_tokens, col_blocks(n_tokens, d)), dim3(256), 0, (cudaStream_t)stream, x, y,
                      (const T*)z, (const TW*)z_bias, mix, share, (const T*)h, state, state_ld, state_rows, slots, n_tokens, streams, d,

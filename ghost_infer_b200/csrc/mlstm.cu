@@ -10,8 +10,12 @@
 // this kernel hands it keep_t and put_t per token and head, and out_t, by which the read-out is multiplied afterwards.
 // Everything here is 32-bit.  Per sequence and head the state holds n (K numbers) and m.
 //
-// grid (heads, sequences), one warp a block: lane l holds entries l, l + 32, ... of n.  The walk is serial in t; the rows of the
-// next tokens do not depend on it, so their loads are issued ahead.
+// grid (heads, sequences), four warps a block.  The tokens of a sequence are taken in chunks: all threads load a chunk's keys,
+// queries and gate rows into shared memory (one trip to memory a chunk) and make i and f; one thread walks m through the chunk
+// (a maximum and an addition a token); keep and put follow for all tokens at once; one warp walks n (lane l holds entries l,
+// l + 32, ... in registers: two multiply-adds an entry and token, the lanes' shares of n . q left in shared memory); the
+// shares are added per token in a fixed order.  The arithmetic of a token does not depend on where the chunks begin, so a
+// prompt cut anywhere gives the same bits.
 #include <math.h>
 
 #include "api.h"
@@ -19,64 +23,110 @@
 
 namespace {
 
-constexpr int ML_MAX_PER_LANE = 16;      // keys of up to 512 numbers
-
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T>
-__global__ void __launch_bounds__(32)
+template <typename T, int NPL, int CH>
+__global__ void __launch_bounds__(128)
 mlstm_gates_kernel(float* __restrict__ keep_out, float* __restrict__ put_out, float* __restrict__ scale_out, const T* q, long ldq,
                    const T* k, long ldk, const T* gi_in, const T* gf_in, long ldg, const float* __restrict__ bi,
                    const float* __restrict__ bf, float cap, float q_scale, float* state, long state_ld, int state_rows,
                    const int* cu_seqlens, const int* seq_slots, int heads, int K) {
+  extern __shared__ float sm[];
+  constexpr int Kp = NPL * 32;
+  float* sk = sm;                    // [CH][Kp]
+  float* sq = sk + CH * Kp;          // [CH][Kp]
+  float* sdot = sq + CH * Kp;        // [CH][33]
+  float* si = sdot + CH * 33;        // [CH] log input gates, then put
+  float* sf = si + CH;               // [CH] log forget gates, then keep
+  float* smx = sf + CH;              // [CH] m after each token
+  float* spv = smx + CH;             // [CH] m before each token
+  __shared__ float m_carry;
   gi::pdl_prologue();
-  const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
   if (qlen <= 0) return;
   const int slot = seq_slots[b];
   float* st = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + (size_t)h * (K + 1);
-  float n[ML_MAX_PER_LANE];
+  float n[NPL];
 #pragma unroll
-  for (int i = 0; i < ML_MAX_PER_LANE; ++i) {
+  for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
-    n[i] = e < K ? st[e] : 0.f;
+    n[i] = (warp == 0 && e < K) ? st[e] : 0.f;
   }
-  float m = st[K];
+  if (tid == 0) m_carry = st[K];
   const float bias_i = bi != nullptr ? bi[h] : 0.f, bias_f = bf != nullptr ? bf[h] : 0.f;
-  for (int t = 0; t < qlen; ++t) {
-    const size_t tok = (size_t)tok0 + t;
-    float kk[ML_MAX_PER_LANE], qq[ML_MAX_PER_LANE];
+  for (int c0 = 0; c0 < qlen; c0 += CH) {
+    const int nh = min(CH, qlen - c0);
+    const size_t tokc = (size_t)tok0 + c0;
+    for (int idx = tid; idx < nh * Kp; idx += 128) {
+      const int t = idx / Kp, e = idx % Kp;
+      sk[idx] = e < K ? gi::ldf(k + (tokc + t) * ldk + (size_t)h * K + e) : 0.f;
+      sq[idx] = e < K ? gi::ldf(q + (tokc + t) * ldq + (size_t)h * K + e) : 0.f;
+    }
+    if (tid < nh) {
+      const float a = gi::ldf(gi_in + (tokc + tid) * ldg + h) + bias_i, bb = gi::ldf(gf_in + (tokc + tid) * ldg + h) + bias_f;
+      si[tid] = cap * tanhf(a / cap);
+      sf[tid] = log_sigmoid_f(cap * tanhf(bb / cap));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float m = m_carry;
+      for (int t = 0; t < nh; ++t) {
+        spv[t] = m;
+        m = fmaxf(sf[t] + m, si[t]);
+        smx[t] = m;
+      }
+      m_carry = m;
+    }
+    __syncthreads();
+    if (tid < nh) {
+      const float keep = expf(sf[tid] + spv[tid] - smx[tid]), put = expf(si[tid] - smx[tid]);
+      sf[tid] = keep;
+      si[tid] = put;
+      keep_out[(tokc + tid) * heads + h] = keep;
+      put_out[(tokc + tid) * heads + h] = put;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      for (int t = 0; t < nh; ++t) {
+        const float keep = sf[t], put = si[t];
+        float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < ML_MAX_PER_LANE; ++i) {
+        for (int i = 0; i < NPL; ++i) {
+          n[i] = fmaf(put, sk[t * Kp + lane + 32 * i], keep * n[i]);
+          dot = fmaf(n[i], sq[t * Kp + lane + 32 * i], dot);
+        }
+        sdot[t * 33 + lane] = dot;
+      }
+    }
+    __syncthreads();
+    if (tid < nh) {
+      float d = 0.f;
+      for (int l = 0; l < 32; ++l) d += sdot[tid * 33 + l];
+      d *= q_scale;
+      scale_out[(tokc + tid) * heads + h] = q_scale / (fmaxf(fabsf(d), expf(-smx[tid])) + 1e-6f);
+    }
+    __syncthreads();
+  }
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
       const int e = lane + 32 * i;
-      kk[i] = e < K ? gi::ldf(k + tok * ldk + (size_t)h * K + e) : 0.f;
-      qq[i] = e < K ? gi::ldf(q + tok * ldq + (size_t)h * K + e) : 0.f;
-    }
-    const float a = gi::ldf(gi_in + tok * ldg + h) + bias_i, bb = gi::ldf(gf_in + tok * ldg + h) + bias_f;
-    const float ig = cap * tanhf(a / cap);
-    const float fg = log_sigmoid_f(cap * tanhf(bb / cap));
-    const float m_new = fmaxf(fg + m, ig);
-    const float keep = expf(fg + m - m_new), put = expf(ig - m_new);
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < ML_MAX_PER_LANE; ++i) {
-      n[i] = fmaf(put, kk[i], keep * n[i]);
-      dot = fmaf(n[i], qq[i], dot);
-    }
-    dot = gi::warp_sum(dot) * q_scale;
-    m = m_new;
-    if (lane == 0) {
-      keep_out[tok * heads + h] = keep;
-      put_out[tok * heads + h] = put;
-      scale_out[tok * heads + h] = q_scale / (fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f);
+      if (e < K) st[e] = n[i];
     }
   }
-#pragma unroll
-  for (int i = 0; i < ML_MAX_PER_LANE; ++i) {
-    const int e = lane + 32 * i;
-    if (e < K) st[e] = n[i];
-  }
-  if (lane == 0) st[K] = m;
+  if (tid == 0) st[K] = m_carry;
+}
+
+template <typename T, int NPL, int CH>
+cudaError_t launch_gates(dim3 grid, cudaStream_t s, float* keep, float* put, float* out_scale, const void* q, long ldq, const void* k,
+                         long ldk, const void* gate_i, const void* gate_f, long ldg, const float* bias_i, const float* bias_f, float cap,
+                         float q_scale, float* state, long state_ld, int state_rows, const int* cu_seqlens, const int* seq_slots,
+                         int heads, int K) {
+  const size_t smem = (size_t)(2 * CH * NPL * 32 + CH * 33 + 4 * CH) * sizeof(float);
+  return gi::launch(mlstm_gates_kernel<T, NPL, CH>, grid, dim3(128), smem, s, keep, put, out_scale, (const T*)q, ldq, (const T*)k, ldk,
+                    (const T*)gate_i, (const T*)gate_f, ldg, bias_i, bias_f, cap, q_scale, state, state_ld, state_rows, cu_seqlens,
+                    seq_slots, heads, K);
 }
 
 }  // namespace
@@ -86,13 +136,21 @@ extern "C" int gi_mlstm_gates(float* keep, float* put, float* out_scale, const v
                               float cap, float q_scale, float* state, long state_ld, int state_rows, const int* cu_seqlens,
                               const int* seq_slots, int n_seqs, int heads, int K, void* stream) {
   if (n_seqs <= 0) return GI_OK;
-  if (heads <= 0 || K <= 0 || K > 32 * ML_MAX_PER_LANE) return gi::fail(GI_ERR_UNSUPPORTED, "mlstm_gates: keys of %d numbers (at most %d)", K, 32 * ML_MAX_PER_LANE);
+  if (heads <= 0 || K <= 0 || K > 512) return gi::fail(GI_ERR_UNSUPPORTED, "mlstm_gates: keys of %d numbers (at most 512)", K);
   if (!(cap > 0.f)) return gi::fail(GI_ERR_ARG, "mlstm_gates: the gates' cap must be positive");
   if (state_ld < (long)heads * (K + 1)) return gi::fail(GI_ERR_ARG, "mlstm_gates: state rows of %ld floats, wanted %ld", state_ld, (long)heads * (K + 1));
   cudaError_t e = cudaSuccess;
-  GI_DISPATCH_DTYPE(dtype, T,
-      e = gi::launch(mlstm_gates_kernel<T>, dim3(heads, n_seqs), dim3(32), 0, (cudaStream_t)stream, keep, put, out_scale, (const T*)q, ldq,
-                     (const T*)k, ldk, (const T*)gate_i, (const T*)gate_f, ldg, bias_i, bias_f, cap, q_scale, state, state_ld, state_rows,
-                     cu_seqlens, seq_slots, heads, K));
+  const dim3 grid(heads, n_seqs);
+  cudaStream_t s = (cudaStream_t)stream;
+#define GI_GATES(NPL, CH)                                                                                                      \
+  GI_DISPATCH_DTYPE(dtype, T, e = (launch_gates<T, NPL, CH>(grid, s, keep, put, out_scale, q, ldq, k, ldk, gate_i, gate_f, ldg, \
+                                                            bias_i, bias_f, cap, q_scale, state, state_ld, state_rows,          \
+                                                            cu_seqlens, seq_slots, heads, K)))
+  if (K <= 32) GI_GATES(1, 32);
+  else if (K <= 64) GI_GATES(2, 32);
+  else if (K <= 128) GI_GATES(4, 32);
+  else if (K <= 256) GI_GATES(8, 16);
+  else GI_GATES(16, 8);
+#undef GI_GATES
   return gi::check(e, "mlstm_gates");
 }

@@ -122,6 +122,7 @@ def _bind():
         "gi_stream_expand": [P, P, I, I, I, P],
         "gi_stream_sum": [P, P, P, I, I, I, P],
         "gi_hyper_read": [P, I, P, P, P, I, P, I, I, I, F, P],
+        "gi_hyper_read_conv": [P, I, P, P, P, I, P, I, I, I, F, P, P, I, P, L, I, P, I, P],
         "gi_input_conv": [P, P, I, P, I, P, L, I, P, I, I, I, P],
         "gi_hyper_write": [P, P, P, P, I, I, P, P, P, P, L, I, P, I, I, I, I, P],
         "gi_scale_rows": [P, F, L, P],
@@ -2182,9 +2183,16 @@ def stream_sum(x: torch.Tensor, streams: int, rows: Optional[torch.Tensor] = Non
     return out
 
 
+def hyper_read_conv_ok(d: int, taps: int) -> bool:
+    """Whether `hyper_read` can run the input convolution of a one-token step in the same launch."""
+    return d % 4 == 0 and 1 <= taps <= 8
+
+
 def hyper_read(x: torch.Tensor, blend: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
-               zero: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """h = rmsnorm(sum_s blend[s] x[:, s]) * weight in `out_dtype`; `zero` (float32 [tokens, d]) is set to zero in the same pass."""
+               zero: Optional[torch.Tensor] = None, conv=None):
+    """h = rmsnorm(sum_s blend[s] x[:, s]) * weight in `out_dtype`; `zero` (float32 [tokens, d]) is set to zero in the same pass.
+    `conv` = (taps_w, state, step), only for a step of one token a sequence and where `hyper_read_conv_ok`: the input
+    convolution (`input_conv`) runs in the same launch and (h, h + conv(h)) is returned."""
     lib = _bind()
     _cuda(x, "residual streams")
     streams = blend.numel()
@@ -2196,6 +2204,18 @@ def hyper_read(x: torch.Tensor, blend: torch.Tensor, weight: torch.Tensor, eps: 
     if zero is not None and (zero.dtype != torch.float32 or tuple(zero.shape) != (n, d) or not zero.is_contiguous()):
         raise KernelError("hyper_read: the rows to zero must be contiguous float32 [tokens, width]")
     h = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    if conv is not None:
+        taps_w, state, step = conv
+        taps = taps_w.shape[1]
+        if not step.is_decode or tuple(taps_w.shape) != (d, taps) or not taps_w.is_contiguous() or not hyper_read_conv_ok(d, taps):
+            raise KernelError("hyper_read: the convolution rides along in steps of one token a sequence, with taps [width, taps]")
+        sp, sld, srows = _conv_state(state, taps, d)
+        c = torch.empty((n, d), dtype=out_dtype, device=x.device)
+        _check(lib, lib.gi_hyper_read_conv(h.data_ptr(), _DT[out_dtype], x.data_ptr(), blend.data_ptr(), weight.data_ptr(),
+                                           _dt(weight, "norm weight"), zero.data_ptr() if zero is not None else None, n, streams, d,
+                                           float(eps), c.data_ptr(), taps_w.data_ptr(), _dt(taps_w, "taps"), sp, sld, srows,
+                                           _i32(step.token_slots, "slots"), taps, _stream()))
+        return h, c
     _check(lib, lib.gi_hyper_read(h.data_ptr(), _DT[out_dtype], x.data_ptr(), blend.data_ptr(), weight.data_ptr(), _dt(weight, "norm weight"),
                                   zero.data_ptr() if zero is not None else None, n, streams, d, float(eps), _stream()))
     return h

@@ -82,15 +82,20 @@ class HyperConnections(Block):
         dt = norm.rt.dtype
         n, d = x.shape[0], conn.width
         y = torch.empty((n, d), dtype=torch.float32, device=x.device)
-        with ops.bucket("norm"):
-            h = ops.hyper_read(x, conn.blend, norm.weight, norm.eps, dt, zero=y)
         state = None
         if conn.taps > 1:
             if memory.block_state is None:
                 raise RuntimeError("the input convolution was given no per-sequence state")
             state = memory.block_state[:, which]
-        with ops.bucket("conv"):
-            c = ops.input_conv(h, conn.conv_w, state, step) if conn.taps else h
+        if conn.taps and step.is_decode and ops.hyper_read_conv_ok(d, conn.taps):
+            # one token a sequence: every older input comes from the state, and the convolution rides in the reading pass
+            with ops.bucket("norm"):
+                h, c = ops.hyper_read(x, conn.blend, norm.weight, norm.eps, dt, zero=y, conv=(conn.conv_w, state, step))
+        else:
+            with ops.bucket("norm"):
+                h = ops.hyper_read(x, conn.blend, norm.weight, norm.eps, dt, zero=y)
+            with ops.bucket("conv"):
+                c = ops.input_conv(h, conn.conv_w, state, step) if conn.taps else h
         with ops.bucket("out matmul"):
             z = linear(h, conn.w_gate, out_dtype=dt) if conn.gate else None
         run(c, y)
