@@ -544,6 +544,12 @@ int gi_attn_prefill_t5_ex2(void* out, long ldo, const void* q, long ldq, long q_
                            const void* vcache, long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens,
                            const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                            float scale, int window, float softcap, const float* sinks, int chunk, int keep_first, void* stream);
+// gi_clamped_glu over rows whose gate and up columns are interleaved in blocks of 8 ([8 gate | 8 up] ...), if `interleaved`.
+int gi_clamped_glu_rows(void* out, const void* in, long ld_in, int dtype, int n_rows, int f, float limit, float alpha, int interleaved,
+                        void* stream);
+// gi_gemm_stream_bf16's gated mode with the clamped form of the gated value (a product of up to 64 rows).
+int gi_gemm_stream_bf16_clamped(void* out, const void* A, const void* W, float* scratch, int* counters, int n_counters, int M, int N,
+                                int K, long lda, long ldw, long ldo, float limit, float alpha, void* stream);
 // gi_gemm_tc_bf16's gated mode with the clamped form of the gated value (see gi_clamped_glu); W's gate and up rows interleaved
 // in blocks of 8.  And a prompt step's clamped gated experts through it, stretch by stretch (see gi_moe_experts_tc).
 int gi_gemm_tc_bf16_clamped(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo, int tile_n,

@@ -53,7 +53,8 @@ __device__ int g_stream_status = 0;
 struct Next {
   int N, K, n_ctas, units_ahead, all_shared;
   unsigned long long* timeline;   // this launch's [TL_BLOCKS][TL_EVENTS] stamps, or null
-  int act;                        // this launch's own gated epilogue: 0 silu, 1 gelu (tanh form)
+  int act;                        // this launch's own gated epilogue: 0 silu, 1 gelu (tanh form), 4 the clamped form
+  float limit, alpha;             // of the clamped form (see gi::clamped_glu_bf16)
 };
 
 struct Range {
@@ -356,7 +357,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
             for (int j = 0; j < GROUP; ++j) {
               const float up = __shfl_down_sync(0xffffffffu, v[m0 + j], 8);
-              h[j] = gi::gated_mul_bf16(v[m0 + j], up, next.act);
+              h[j] = next.act == 4 ? gi::clamped_glu_bf16(v[m0 + j], up, next.limit, next.alpha) : gi::gated_mul_bf16(v[m0 + j], up, next.act);
             }
             if (is_gate && f < N) {
 #pragma unroll
@@ -476,11 +477,31 @@ extern "C" int gi_gemm_stream_bf16(void* out, int mode, const void* A, const voi
   return gi_gemm_stream_bf16_ex(out, mode, A, W, scratch, counters, n_counters, M, N, K, lda, ldw, ldo, use_pdl, nullptr, 0, 0, 0, 0, 0, stream);
 }
 
+static int gemm_stream_any(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters, int M,
+                           int N, int K, long lda, long ldw, long ldo, int use_pdl, const void* next_W, int next_N, int next_K,
+                           long next_ldw, int next_mode, int units_ahead, float limit, float alpha, void* stream);
+
 extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const void* W, float* scratch, int* counters,
                                       int n_counters, int M, int N, int K, long lda, long ldw, long ldo, int use_pdl,
                                       const void* next_W, int next_N, int next_K, long next_ldw, int next_mode,
                                       int units_ahead, void* stream) {
-  const int act = (mode & GI_ACT_GELU) ? 1 : 0;
+  return gemm_stream_any(out, mode, A, W, scratch, counters, n_counters, M, N, K, lda, ldw, ldo, use_pdl, next_W, next_N, next_K, next_ldw,
+                         next_mode, units_ahead, 0.f, 1.f, stream);
+}
+
+// The gated product (GI_SKINNY_SWIGLU's layout of W and of the output) with the clamped form of the gated value:
+// min(g, limit) * sigmoid(alpha * that) * (clamp(u, -limit, limit) + 1).
+extern "C" int gi_gemm_stream_bf16_clamped(void* out, const void* A, const void* W, float* scratch, int* counters, int n_counters,
+                                           int M, int N, int K, long lda, long ldw, long ldo, float limit, float alpha, void* stream) {
+  if (!(limit > 0.f)) return gi::fail(GI_ERR_ARG, "streamed product: the clamped form needs a positive limit");
+  return gemm_stream_any(out, GI_SKINNY_SWIGLU, A, W, scratch, counters, n_counters, M, N, K, lda, ldw, ldo, -1, nullptr, 0, 0, 0, 0, 0,
+                         limit, alpha, stream);
+}
+
+static int gemm_stream_any(void* out, int mode, const void* A, const void* W, float* scratch, int* counters, int n_counters, int M,
+                           int N, int K, long lda, long ldw, long ldo, int use_pdl, const void* next_W, int next_N, int next_K,
+                           long next_ldw, int next_mode, int units_ahead, float limit, float alpha, void* stream) {
+  const int act = limit > 0.f ? 4 : ((mode & GI_ACT_GELU) ? 1 : 0);
   mode &= 0xff;
   next_mode &= 0xff;
   if (act && mode != GI_SKINNY_SWIGLU) return gi::fail(GI_ERR_ARG, "streamed product: an activation without a gated mode");
@@ -501,12 +522,12 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
   rc = gi::tensor_map_2d(&ma, A, M, K, lda, nt);
   if (rc != GI_OK) return rc;
   // the next product's matrix, if the caller knows it and it can have a tensor map; otherwise nothing is fetched ahead
-  Next next = {0, 0, 0, 0, 0, nullptr, act};
+  Next next = {0, 0, 0, 0, 0, nullptr, act, limit, alpha};
   CUtensorMap mn = mw;
   if (next_W && units_ahead > 0 && next_N > 0 && next_K > 0 && next_K % 8 == 0 && next_ldw % 8 == 0 && !((uintptr_t)next_W & 15) &&
       gi::tensor_map_2d(&mn, next_W, next_N, next_K, next_ldw, TILE_ROWS) == GI_OK) {
     next = {next_N, next_K, grid_for(next_N, next_K, next_mode), units_ahead,
-            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr, act};
+            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr, act, limit, alpha};
   } else {
     mn = mw;
   }

@@ -127,12 +127,15 @@ scaled_norm_gate_kernel(T* __restrict__ out, const float* y, const float* s, con
 }
 
 template <typename T>
-__global__ void clamped_glu_kernel(T* __restrict__ out, const T* in, long ld_in, int f, float limit, float alpha, size_t total) {
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* in, long ld_in, int f, float limit, float alpha, size_t total,
+                                   int interleaved) {
   gi::pdl_prologue();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / f, c = i % f;
-  float g = gi::ldf(in + t * ld_in + c), u = gi::ldf(in + t * ld_in + f + c);
+  // gate and up of output c: columns c and f + c, or, interleaved in blocks of 8, (c / 8) * 16 + c % 8 and 8 further
+  const size_t gc = interleaved ? (c / 8) * 16 + c % 8 : c;
+  float g = gi::ldf(in + t * ld_in + gc), u = gi::ldf(in + t * ld_in + (interleaved ? gc + 8 : f + c));
   if (limit > 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
@@ -194,11 +197,17 @@ extern "C" int gi_scaled_norm_gate(void* out, int dtype, const float* y, const f
 }
 
 extern "C" int gi_clamped_glu(void* out, const void* in, long ld_in, int dtype, int n_rows, int f, float limit, float alpha, void* stream) {
+  return gi_clamped_glu_rows(out, in, ld_in, dtype, n_rows, f, limit, alpha, 0, stream);
+}
+
+extern "C" int gi_clamped_glu_rows(void* out, const void* in, long ld_in, int dtype, int n_rows, int f, float limit, float alpha,
+                                   int interleaved, void* stream) {
   if (n_rows <= 0 || f <= 0) return GI_OK;
+  if (interleaved && f % 8) return gi::fail(GI_ERR_ARG, "clamped_glu: interleaved rows need a width that is a multiple of 8");
   const size_t total = (size_t)n_rows * f;
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
       e = gi::launch(clamped_glu_kernel<T>, dim3(blocks_of(total)), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)in, ld_in, f,
-                     limit, alpha, total));
+                     limit, alpha, total, interleaved));
   return gi::check(e, "clamped_glu");
 }

@@ -58,10 +58,22 @@ mlstm_gates_kernel(float* __restrict__ keep_out, float* __restrict__ put_out, fl
   for (int c0 = 0; c0 < qlen; c0 += CH) {
     const int nh = min(CH, qlen - c0);
     const size_t tokc = (size_t)tok0 + c0;
-    for (int idx = tid; idx < nh * Kp; idx += 128) {
-      const int t = idx / Kp, e = idx % Kp;
-      sk[idx] = e < K ? gi::ldf(k + (tokc + t) * ldk + (size_t)h * K + e) : 0.f;
-      sq[idx] = e < K ? gi::ldf(q + (tokc + t) * ldq + (size_t)h * K + e) : 0.f;
+    {
+      // every load of the chunk before anything is stored: one trip to memory a chunk
+      constexpr int R = CH * Kp / 128;
+      float kr[R], qr[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int idx = tid + i * 128, t = idx / Kp, e = idx % Kp;
+        const bool live = t < nh && e < K;
+        kr[i] = live ? gi::ldf(k + (tokc + t) * ldk + (size_t)h * K + e) : 0.f;
+        qr[i] = live ? gi::ldf(q + (tokc + t) * ldq + (size_t)h * K + e) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        sk[tid + i * 128] = kr[i];
+        sq[tid + i * 128] = qr[i];
+      }
     }
     if (tid < nh) {
       const float a = gi::ldf(gi_in + (tokc + tid) * ldg + h) + bias_i, bb = gi::ldf(gf_in + (tokc + tid) * ldg + h) + bias_f;

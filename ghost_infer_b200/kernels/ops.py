@@ -130,6 +130,9 @@ def _bind():
         "gi_head_gate": [P, P, I, P, L, I, I, I, P],
         "gi_scaled_norm_gate": [P, I, P, P, P, L, P, I, I, I, I, F, P],
         "gi_clamped_glu": [P, P, L, I, I, I, F, F, P],
+        "gi_clamped_glu_rows": [P, P, L, I, I, I, F, F, I, P],
+        "gi_gemm_stream_bf16_clamped": [P, P, P, P, P, I, I, I, I, L, L, L, F, F, P],
+        "gi_gemm_tc_bf16_clamped": [P, P, P, I, I, I, L, L, L, I, F, F, P],
         "gi_moe_route_shares": [P, P, P, P, I, L, P, P, I, I, I, I, I, I, P, F, P],
         "gi_moe_gemm_gate_up_clamped": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, I, F, F, P],
         "gi_attn_prefill_generic_ex3": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, L, I, P],
@@ -2347,17 +2350,42 @@ def scaled_norm_gate(y: torch.Tensor, scale: Optional[torch.Tensor], gate: torch
     return out
 
 
-def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
-    """rows [gate | up] -> min(gate, limit) * sigmoid(alpha * that) * (clamp(up, -limit, limit) + 1), in the rows' type."""
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, interleaved: bool = False) -> torch.Tensor:
+    """rows [gate | up] (or, `interleaved`, blocks [8 gate | 8 up]) -> min(gate, limit) * sigmoid(alpha * that) *
+    (clamp(up, -limit, limit) + 1), in the rows' type."""
     lib = _bind()
     _cuda(gate_up, "gate/up rows")
     if gate_up.dim() != 2 or gate_up.stride(1) != 1 or gate_up.shape[1] % 2:
         raise KernelError("gate/up rows must be a [rows, 2 * width] matrix")
     n, f = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((n, f), dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib, lib.gi_clamped_glu(out.data_ptr(), gate_up.data_ptr(), gate_up.stride(0), _dt(gate_up, "gate/up rows"), n, f, float(limit),
-                                   float(alpha), _stream()))
+    _check(lib, lib.gi_clamped_glu_rows(out.data_ptr(), gate_up.data_ptr(), gate_up.stride(0), _dt(gate_up, "gate/up rows"), n, f,
+                                        float(limit), float(alpha), int(interleaved), _stream()))
     return out
+
+
+def clamped_glu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """The clamped gated value of (W_gate h, W_up h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]: in
+    the products' epilogues (streamed for up to 64 rows, tcgen05 tiles above), or as a step of its own where neither product
+    takes the operands or there is no positive limit."""
+    lib = _bind()
+    m, k = h.shape
+    n = w_interleaved.shape[0]
+    if limit and limit > 0 and n % 16 == 0:
+        if skinny_ok(h, w_interleaved) and USE_STREAM and (n + 127) // 128 <= _STREAM_COUNTERS:
+            out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=h.device)
+            scratch, counters = _stream_buffers(h.device)
+            _check(lib, lib.gi_gemm_stream_bf16_clamped(out.data_ptr(), h.data_ptr(), w_interleaved.data_ptr(), scratch.data_ptr(),
+                                                        counters.data_ptr(), counters.numel(), m, n, k, h.stride(0), w_interleaved.stride(0),
+                                                        out.stride(0), float(limit), float(alpha), _stream()))
+            return out
+        if tc_ok(h, w_interleaved) and m > SKINNY_MAX_ROWS:
+            out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=h.device)
+            _check(lib, lib.gi_gemm_tc_bf16_clamped(out.data_ptr(), h.data_ptr(), w_interleaved.data_ptr(), m, n, k, h.stride(0),
+                                                    w_interleaved.stride(0), out.stride(0), int(TC_TILE_N), float(limit), float(alpha),
+                                                    _stream()))
+            return out
+    return clamped_glu(linear(h, w_interleaved, out_dtype=h.dtype), limit, alpha, interleaved=True)
 
 
 def moe_route_shares(h: torch.Tensor, w_router: torch.Tensor, top: int, correction: Optional[torch.Tensor], weight_scale: float):

@@ -266,7 +266,14 @@ class ShareRoutedExperts(FeedForward):
             g, u = rt.place(tensors[s + "gate"]), rt.place(tensors[s + "up"])
             if g.dtype != u.dtype:
                 g, u = g.float(), u.float()
-            self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
+            f = self.shared_ff
+            # 16-bit path: gate and up rows in blocks of 8, so that the products' gated epilogues hold both halves of a value
+            self.shared_interleaved = (rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and f % 8 == 0 and rt.device.type == "cuda")
+            if self.shared_interleaved:
+                self.w_shared_gu = torch.stack([g.view(f // 8, 8, self.hidden), u.view(f // 8, 8, self.hidden)], dim=1) \
+                    .reshape(2 * f, self.hidden).contiguous()
+            else:
+                self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
             self.w_shared_down = rt.place(tensors[s + "down"])
 
     # rows per expert, on average, from which a prompt step takes the tensor-core products expert by expert
@@ -291,6 +298,9 @@ class ShareRoutedExperts(FeedForward):
         with ops.bucket("ffn matmul"):
             ops.settle(residual)
             if self.shared_ff:
-                act = ops.clamped_glu(linear(h, self.w_shared_gu, out_dtype=self.rt.dtype), self.shared_limit, self.alpha)
+                if self.shared_interleaved:
+                    act = ops.clamped_glu_interleaved(h, self.w_shared_gu, self.shared_limit, self.alpha)
+                else:
+                    act = ops.clamped_glu(linear(h, self.w_shared_gu, out_dtype=self.rt.dtype), self.shared_limit, self.alpha)
                 linear(act, self.w_shared_down, out=residual, accumulate=True)
             ops.moe_combine(residual, down, inv, wts)

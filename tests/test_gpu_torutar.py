@@ -319,6 +319,8 @@ ALONE = {
     "latent_all_rotated_queries_wide": [layer("latent_attention", lat(2, 8, 8, 8, 16, 40, 0.3, base=50.0))],
     "matrix_memory": [layer("mlstm", mem(3, 6, 9, 12.0))],
     "matrix_memory_tight_cap": [layer("mlstm", mem(2, 4, 4, 0.5))],
+    "matrix_memory_wide_keys": [layer("mlstm", mem(1, 200, 8, 10.0))],
+    "matrix_memory_widest_keys": [layer("mlstm", mem(1, 300, 4, 10.0))],
     "experts": [layer("mlstm", mem(1, 4, 4, 5.0), moe(6, 2, 10, 1.0, 12, 2.0, 2.0))],
     "experts_all_chosen_no_clamp_reached": [layer("mlstm", mem(1, 4, 4, 5.0), moe(3, 3, 8, 50.0, 4, 50.0, 1.0))],
 }
@@ -362,6 +364,42 @@ def test_the_matrix_memory_and_the_routers_choice_by_themselves():
     rid, rw = pt.route(h, w, "l0.mlp.", cfg["layers"][0]["mlp"]["router"])
     assert np.array_equal(ids.cpu().numpy(), rid)
     assert np.abs(wts.cpu().numpy() - rw).max() <= 1e-5
+
+
+@pytest.mark.parametrize("rows", [5, 64, 65, 300])
+@pytest.mark.parametrize("limit", [0.6, 7.0])
+def test_clamped_gated_value_in_the_products(rows, limit):
+    """min(g, limit) * sigmoid(alpha g') * (clamp(u) + 1) in the epilogue of the streamed product (up to 64 rows) and of the
+    tcgen05 product (more), and as a step of its own over either layout of the rows, against 64-bit torch."""
+    from ghost_infer_b200.kernels import ops
+    g = torch.Generator(device="cuda:0").manual_seed(rows)
+    k, f, alpha = 128, 72, 1.702
+    h = torch.randn((rows, k), device="cuda:0", generator=g).bfloat16()
+    wg, wu = (torch.randn((f, k), device="cuda:0", generator=g) * 0.15).bfloat16(), (torch.randn((f, k), device="cuda:0", generator=g) * 0.15).bfloat16()
+    gate, up = h.double() @ wg.double().T, h.double() @ wu.double().T
+    gc, uc = gate.clamp(max=limit), up.clamp(-limit, limit)
+    ref = gc * torch.sigmoid(alpha * gc) * (uc + 1.0)
+    inter = torch.stack([wg.view(f // 8, 8, k), wu.view(f // 8, 8, k)], dim=1).reshape(2 * f, k).contiguous()
+    got = ops.clamped_glu_interleaved(h, inter, limit, alpha)
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (rows, f)
+    torch.testing.assert_close(got.double(), ref, rtol=2e-2, atol=2e-2)
+    rows32 = torch.cat([gate, up], dim=1).float().contiguous()
+    torch.testing.assert_close(ops.clamped_glu(rows32, limit, alpha).double(), ref, rtol=1e-5, atol=1e-5)
+    inter32 = torch.stack([gate.view(rows, f // 8, 8), up.view(rows, f // 8, 8)], dim=2).reshape(rows, 2 * f).float().contiguous()
+    torch.testing.assert_close(ops.clamped_glu(inter32, limit, alpha, interleaved=True).double(), ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_of_a_long_prompt(dtype):
+    """Enough rows per expert for the products expert by expert on the tensor cores (16 bits), and more (token, expert) pairs
+    than the few-row kernels take (both precisions)."""
+    cfg = model_cfg(64, 80, 2, 2, [layer("mlstm", mem(2, 8, 8, 6.0), moe(4, 2, 64, 1.0, 64, 2.0, 1.5))])
+    w = pt.random_weights(cfg, seed=23)
+    eng = engine_of(cfg, tensors_of(w, dtype == "bfloat16"), dtype, max_tokens=1024, max_seq_len=1024)
+    t = np.random.default_rng(3).integers(0, 80, size=400).tolist()
+    gaps = []
+    ref = pt.forward(cfg, w, t, gaps=gaps)
+    check(run_whole(eng, t), ref, dtype, "long prompt", np.min(np.stack(gaps), axis=0) >= 0.01)
 
 
 # ---- whole prompts, decoding, portions, batches -----------------------------------------------------------------------
