@@ -320,7 +320,7 @@ ALONE = {
     "matrix_memory": [layer("mlstm", mem(3, 6, 9, 12.0))],
     "matrix_memory_tight_cap": [layer("mlstm", mem(2, 4, 4, 0.5))],
     "matrix_memory_wide_keys": [layer("mlstm", mem(1, 200, 8, 10.0))],
-    "matrix_memory_widest_keys": [layer("mlstm", mem(1, 300, 4, 10.0))],
+    "matrix_memory_widest_keys": [layer("mlstm", mem(1, 256, 4, 10.0))],
     "experts": [layer("mlstm", mem(1, 4, 4, 5.0), moe(6, 2, 10, 1.0, 12, 2.0, 2.0))],
     "experts_all_chosen_no_clamp_reached": [layer("mlstm", mem(1, 4, 4, 5.0), moe(3, 3, 8, 50.0, 4, 50.0, 1.0))],
 }
