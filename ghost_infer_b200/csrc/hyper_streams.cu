@@ -205,32 +205,47 @@ hyper_read4_kernel(TO* __restrict__ h, const float* x, const float* __restrict__
   }
 }
 
-template <typename T, typename TW>
+// TAPS > 0: the number of taps is known when the kernel is compiled, and a thread's 4 x TAPS weights arrive as TAPS loads of
+// four numbers into registers; TAPS 0: any number of taps, the weights read one by one.
+template <typename T, typename TW, int TAPS>
 __global__ void __launch_bounds__(256)
 input_conv4_kernel(T* __restrict__ out, const T* h, const TW* __restrict__ k, const float* state, long state_ld, int state_rows,
-                   const int* slots, int d, int taps) {
+                   const int* slots, int d, int taps_arg) {
   gi::pdl_prologue();
+  const int taps = TAPS > 0 ? TAPS : taps_arg;
   const int t = blockIdx.x;
   const int slot = slots[t];
   const int q = rows_before(slots, t, taps - 1);
   const float* st = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld;
   for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < d; c += gridDim.y * 1024) {
+    float kw[TAPS > 0 ? 4 * TAPS : 1];
+    if (TAPS > 0) {
+#pragma unroll
+      for (int i = 0; i < TAPS; ++i) {
+        const float4 w4 = gi::ld4(k + (size_t)c * TAPS + 4 * i);
+        kw[4 * i] = w4.x; kw[4 * i + 1] = w4.y; kw[4 * i + 2] = w4.z; kw[4 * i + 3] = w4.w;
+      }
+    }
     const float4 o4 = gi::ld4(h + (size_t)t * d + c);
     const float own[4] = {o4.x, o4.y, o4.z, o4.w};
     float acc[4] = {own[0], own[1], own[2], own[3]};
-    for (int j = 0; j < taps; ++j) {
-      const int back = taps - 1 - j;
-      float4 v4 = o4;
-      if (back > 0) v4 = back <= q ? gi::ld4(h + (size_t)(t - back) * d + c) : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - back + q) * d + c);
-      const float v[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[e] = fmaf(gi::ldf(k + (size_t)(c + e) * taps + j), v[e], acc[e]);
+    for (int j = 0; j < (TAPS > 0 ? TAPS : MAX_TAPS); ++j) {
+      if (j < taps) {
+        const int back = taps - 1 - j;
+        float4 v4 = o4;
+        if (back > 0) v4 = back <= q ? gi::ld4(h + (size_t)(t - back) * d + c) : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - back + q) * d + c);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(TAPS > 0 ? kw[e * (TAPS > 0 ? TAPS : 1) + j] : gi::ldf(k + (size_t)(c + e) * taps + j), v[e], acc[e]);
+      }
     }
     gi::st4(out + (size_t)t * d + c, make_float4(acc[0], acc[1], acc[2], acc[3]));
   }
 }
 
-template <typename T, typename TW>
+// SMAX: the most copies this instance holds in registers (4 or MAX_STREAMS)
+template <typename T, typename TW, int SMAX>
 __global__ void __launch_bounds__(256)
 hyper_write4_kernel(float* x, const float* y, const T* z, const TW* __restrict__ zb, const float* __restrict__ M,
                     const float* __restrict__ o, const T* h, float* state, long state_ld, int state_rows, const int* slots,
@@ -246,14 +261,14 @@ hyper_write4_kernel(float* x, const float* y, const T* z, const TW* __restrict__
       if (zb != nullptr) b = gi::ld4(zb + c);
       v.x *= sigmoid_f(g.x + b.x); v.y *= sigmoid_f(g.y + b.y); v.z *= sigmoid_f(g.z + b.z); v.w *= sigmoid_f(g.w + b.w);
     }
-    float4 old[MAX_STREAMS];
+    float4 old[SMAX];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s)
+    for (int s = 0; s < SMAX; ++s)
       if (s < S) old[s] = *reinterpret_cast<const float4*>(xr + (size_t)s * d + c);
     for (int to = 0; to < S; ++to) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s)
+      for (int s = 0; s < SMAX; ++s)
         if (s < S) {
           const float m = M[s * S + to];
           acc.x = fmaf(m, old[s].x, acc.x); acc.y = fmaf(m, old[s].y, acc.y); acc.z = fmaf(m, old[s].z, acc.z); acc.w = fmaf(m, old[s].w, acc.w);
@@ -364,8 +379,14 @@ extern "C" int gi_input_conv(void* out, const void* h, int dtype, const void* ta
   cudaError_t e = cudaSuccess;
   if (d % 4 == 0 && aligned16(out) && aligned16(h) && aligned16(state) && state_ld % 4 == 0) {
     GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
-        e = gi::launch(input_conv4_kernel<T, TW>, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                       (const T*)h, (const TW*)taps_w, state, state_ld, state_rows, slots, d, taps)));
+        {
+          auto kern = input_conv4_kernel<T, TW, 0>;
+          if (taps == 2) kern = input_conv4_kernel<T, TW, 2>;
+          else if (taps == 3) kern = input_conv4_kernel<T, TW, 3>;
+          else if (taps == 4) kern = input_conv4_kernel<T, TW, 4>;
+          e = gi::launch(kern, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)h,
+                         (const TW*)taps_w, state, state_ld, state_rows, slots, d, taps);
+        }));
     return gi::check(e, "input_conv");
   }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
@@ -384,9 +405,11 @@ extern "C" int gi_hyper_write(float* x, const float* y, const void* z, const voi
   cudaError_t e = cudaSuccess;
   if (d % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(z) && aligned16(z_bias) && aligned16(h) && aligned16(state) && state_ld % 4 == 0) {
     GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
-        e = gi::launch(hyper_write4_kernel<T, TW>, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, x, y,
-                       (const T*)z, (const TW*)z_bias, mix, share, (const T*)h, state, state_ld, state_rows, slots, n_tokens, streams, d,
-                       taps)));
+        {
+          auto kern = streams <= 4 ? hyper_write4_kernel<T, TW, 4> : hyper_write4_kernel<T, TW, MAX_STREAMS>;
+          e = gi::launch(kern, dim3(n_tokens, col_blocks4(d)), dim3(256), 0, (cudaStream_t)stream, x, y, (const T*)z, (const TW*)z_bias,
+                         mix, share, (const T*)h, state, state_ld, state_rows, slots, n_tokens, streams, d, taps);
+        }));
     return gi::check(e, "hyper_write");
   }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
