@@ -570,3 +570,83 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
         want = seq[len(p):]
         assert r.tokens[:len(want)] == want, f"prompt of {len(p)}: {r.tokens} vs {want}"
     assert llm.cache.free_pages == llm.cache.n_pages
+
+
+# ---- the replay program as a user runs it ----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(tmp_path, dtype):
+    """`bin/trace_run` on a model folder: requests whole, tails token by token, and unequal batches decoded together."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from ghost_infer_b200.weights.safetensors_io import save_safetensors
+    from test_gpu_trace_run import build_trace
+    name = "A" if dtype == "bfloat16" else "B"
+    cfg, w, tensors = made(name)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(cfg))
+    save_safetensors(str(folder / "model.safetensors"), tensors)
+    reqs, steps = build_trace({"vocab_size": cfg["vocab"]})
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(64 * 8)], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                       text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert p.stdout.split("\n")[:len(steps)] == [f"done {i}" for i in range(len(steps))]
+    refs = {rid: plain(name, ts) for rid, ts in reqs.items()}
+    place, got, want, keep = {}, [], [], []
+    for s in steps:
+        rows = []
+        for e in s["entries"]:
+            base = place.get(e["id"], 0)
+            rows += [(refs[e["id"][:2]][0][base + k], refs[e["id"][:2]][1][base + k]) for k in e["want"]]
+            place[e["id"]] = base + len(e["tokens"])
+        f = out / f"{s['step']}.f32"
+        if rows:
+            got.append(np.fromfile(f, dtype="<f4").reshape(-1, cfg["vocab"]))
+            want += [r for r, _ in rows]
+            keep += [k for _, k in rows]
+        else:
+            assert not f.exists()
+    check(np.concatenate(got, 0), np.stack(want), dtype, "all steps", np.array(keep))
+
+
+# ---- schedules drawn at random ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_drawn_schedules(name):
+    """One to four requests of 1 to 200 tokens; every step takes some of the live requests and gives each a portion of 1 to 130
+    of its next tokens, so a step holds fresh prompts, portions in mid-sequence and single tokens side by side and some
+    requests sit a step out; the places whose logits are wanted are drawn too.  32-bit, so that every row must agree."""
+    eng = engine_for(name, "float32", max_tokens=64 * 32, max_seq_len=1024)
+    rng = np.random.default_rng(sum(map(ord, name)) + 5)
+    rows = 0
+    for draw in range(5):
+        n_req = int(rng.integers(1, 5))
+        lens = [int(rng.integers(1, 200)) for _ in range(n_req)]
+        seqs = [toks(name, n, int(rng.integers(1 << 30))) for n in lens]
+        refs = [plain(name, t)[0] for t in seqs]
+        slots = [eng.cache.open_slot() for _ in seqs]
+        done = [0] * n_req
+        while any(done[i] < lens[i] for i in range(n_req)):
+            live = [i for i in range(n_req) if done[i] < lens[i]]
+            pick = [i for i in live if rng.random() < 0.7] or [live[0]]
+            entries, wants = [], []
+            for i in pick:
+                n = int(min(lens[i] - done[i], rng.choice([1, 1, 2, 3, 7, 33, 64, 65, 130])))
+                w = sorted(set(int(x) for x in rng.integers(0, n, size=int(rng.integers(0, 3))))) or [n - 1]
+                entries.append(gi.StepEntry(slots[i], seqs[i][done[i]:done[i] + n], w))
+                wants.append((i, done[i], w))
+                done[i] += n
+            lg = eng.step(entries).cpu().numpy()
+            r = 0
+            for i, base, w in wants:
+                for x in w:
+                    check(lg[r:r + 1], refs[i][base + x:base + x + 1], "float32", f"{name} draw {draw}, request {i} of lengths {lens}, place {base + x}")
+                    r += 1
+            rows += r
+        for s in slots:
+            eng.cache.close_slot(s)
+    assert rows > 50 and eng.cache.free_pages == eng.cache.n_pages
