@@ -55,31 +55,40 @@ mlstm_gates_kernel(float* __restrict__ keep_out, float* __restrict__ put_out, fl
   }
   if (tid == 0) m_carry = st[K];
   const float bias_i = bi != nullptr ? bi[h] : 0.f, bias_f = bf != nullptr ? bf[h] : 0.f;
+  // a chunk's rows travel through registers: the next chunk's loads are issued before this chunk's walks begin and land
+  // while they run, so a chunk costs its walks alone
+  constexpr int R = CH * Kp / 128;
+  float kr[R], qr[R], ga = 0.f, gb = 0.f;
+  auto fetch = [&](int c0) {
+    const int nh = min(CH, qlen - c0);
+    const size_t tokc = (size_t)tok0 + c0;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int idx = tid + i * 128, t = idx / Kp, e = idx % Kp;
+      const bool live = t < nh && e < K;
+      kr[i] = live ? gi::ldf(k + (tokc + t) * ldk + (size_t)h * K + e) : 0.f;
+      qr[i] = live ? gi::ldf(q + (tokc + t) * ldq + (size_t)h * K + e) : 0.f;
+    }
+    if (tid < nh) {
+      ga = gi::ldf(gi_in + (tokc + tid) * ldg + h);
+      gb = gi::ldf(gf_in + (tokc + tid) * ldg + h);
+    }
+  };
+  fetch(0);
   for (int c0 = 0; c0 < qlen; c0 += CH) {
     const int nh = min(CH, qlen - c0);
     const size_t tokc = (size_t)tok0 + c0;
-    {
-      // every load of the chunk before anything is stored: one trip to memory a chunk
-      constexpr int R = CH * Kp / 128;
-      float kr[R], qr[R];
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int idx = tid + i * 128, t = idx / Kp, e = idx % Kp;
-        const bool live = t < nh && e < K;
-        kr[i] = live ? gi::ldf(k + (tokc + t) * ldk + (size_t)h * K + e) : 0.f;
-        qr[i] = live ? gi::ldf(q + (tokc + t) * ldq + (size_t)h * K + e) : 0.f;
-      }
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        sk[tid + i * 128] = kr[i];
-        sq[tid + i * 128] = qr[i];
-      }
+    for (int i = 0; i < R; ++i) {
+      sk[tid + i * 128] = kr[i];
+      sq[tid + i * 128] = qr[i];
     }
     if (tid < nh) {
-      const float a = gi::ldf(gi_in + (tokc + tid) * ldg + h) + bias_i, bb = gi::ldf(gf_in + (tokc + tid) * ldg + h) + bias_f;
+      const float a = ga + bias_i, bb = gb + bias_f;
       si[tid] = cap * tanhf(a / cap);
       sf[tid] = log_sigmoid_f(cap * tanhf(bb / cap));
     }
+    if (c0 + CH < qlen) fetch(c0 + CH);
     __syncthreads();
     if (tid == 0) {
       float m = m_carry;
