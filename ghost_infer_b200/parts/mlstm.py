@@ -28,7 +28,6 @@ from .linear import linear
 from .linear_state import _stack
 from .registry import register
 
-# fixed by the design: what is added to the normalizer
 _KEYS = ("q", "k", "v", "i", "i.b", "f", "f.b", "g", "norm", "o")
 
 
